@@ -92,10 +92,13 @@ class KVCache:
                                                   device=self.device)
         # Fixed-size per-sequence state, one row per slot for each entry that asks for some.
         self.state_bytes = [r.state_bytes for r in requests]
-        self._state = {entry: torch.zeros((max_slots, r.state_bytes), dtype=torch.uint8, device=self.device)
+        # (one row more than there are slots: padding rows of a graph step name it, so that a part which
+        # writes its sequences' state in a step leaves every live sequence's row alone)
+        self._state = {entry: torch.zeros((max_slots + 1, r.state_bytes), dtype=torch.uint8, device=self.device)
                        for entry, r in enumerate(requests) if r.state_bytes > 0}
         self.sequences: Dict[int, SequenceRecord] = {}
         self.trash_block = num_blocks         # owned by no sequence
+        self.spare_slot = max_slots           # the state row of no sequence
         self._serial = 0
 
     # ---- storage views ---------------------------------------------------
@@ -116,7 +119,8 @@ class KVCache:
         return self.entry_group[entry][0]
 
     def state(self, entry: int) -> torch.Tensor:
-        """``[max_slots, state_bytes]`` bytes of per-sequence state of one cache entry."""
+        """``[max_slots + 1, state_bytes]`` bytes of per-sequence state of one cache entry (the last row is the
+        spare one of ``spare_slot``)."""
         return self._state[entry]
 
     def bytes_per_token(self) -> int:

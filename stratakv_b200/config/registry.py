@@ -60,7 +60,10 @@ def load_config(model_dir):
     """Read ``config.json`` and return ``(architecture, typed config)``."""
     raw = read_config_json(model_dir)
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]              # (some designs name themselves under 'architecture')
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' one name)")
     arch = resolve_architecture(archs[0])
     return arch, arch.config_class.from_dict(raw)

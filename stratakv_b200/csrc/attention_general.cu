@@ -1,0 +1,228 @@
+// Attention with the head sizes as run-time arguments and the optional mechanisms that the
+// head-size-specialised kernels do not have: biases on the projections, a norm on each value head,
+// values narrower or wider than keys, a bias on the score that grows with the logarithm of the
+// distance, and a gate per head on the output.  Two kernels:
+//
+//   qkv_finish:        float rows [q | k | v | ...] of the fused projection -> queries in the compute
+//                      dtype, keys and (normalised) values in their places of the paged cache;
+//   attention_general: one warp per (token, head) over the sequence's own cached keys, online softmax
+//                      by chunks of 32 keys, everything after the loads in float.
+//
+// score(i, j) = (q_i . k_j) * scale - r1[head] * ln(1 + r2[head] * (i - j))      (r1 null: no such term)
+// visible:      0 <= i - j < window   (window 0: every earlier key)
+// out(i)      = softmax(score) . v  *  sigmoid(gate[i, head])                    (gate null: no gate)
+//
+// Cache layout per entry: keys [block][kv_head][block_size][dim], values [block][kv_head][block_size][vdim].
+// These kernels are the same in every build of the library (no compile-time head size); they serve the
+// float32 path and every shape the specialised bfloat16 kernels do not take.
+#include "common.cuh"
+
+namespace skv {
+
+constexpr int GEN_WARPS = 4;
+constexpr int GEN_MAX_VDIM = 256;                 // a lane keeps vdim / 32 accumulators
+constexpr int GEN_ACC = GEN_MAX_VDIM / 32;
+
+// One token per block.  Per head: value_norm != 0 divides each value head by sqrt(mean(v^2) + eps).
+template <typename T>
+__global__ void __launch_bounds__(128)
+qkv_finish_kernel(const float* __restrict__ qkv, int row_stride, const float* __restrict__ q_bias,
+                  const float* __restrict__ k_bias, const float* __restrict__ v_bias,
+                  const int* __restrict__ positions, const int* __restrict__ token_seq,
+                  const int* __restrict__ block_table, int table_width, T* __restrict__ q_out,
+                  T* __restrict__ k_cache, T* __restrict__ v_cache, int num_heads, int num_kv_heads, int dim,
+                  int vdim, int block_size, int value_norm, float value_eps, int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int q_width = num_heads * dim, k_width = num_kv_heads * dim, v_width = num_kv_heads * vdim;
+    const float* src = qkv + (size_t)t * row_stride;
+    T* q_row = q_out + (size_t)t * q_width;
+    for (int c = threadIdx.x; c < q_width; c += blockDim.x)
+        q_row[c] = from_float<T>(src[c] + (q_bias ? q_bias[c] : 0.0f));
+    if (!write_kv) return;
+    const int pos = positions[t];
+    const int block = block_table[(size_t)token_seq[t] * table_width + pos / block_size];
+    const size_t tile_row = (size_t)block * num_kv_heads * block_size + (pos % block_size);   // of kv head 0
+    const float* k_src = src + q_width;
+    for (int c = threadIdx.x; c < k_width; c += blockDim.x) {
+        const int g = c / dim, d = c - g * dim;
+        k_cache[(tile_row + (size_t)g * block_size) * dim + d] = from_float<T>(k_src[c] + (k_bias ? k_bias[c] : 0.0f));
+    }
+    const float* v_src = k_src + k_width;
+    if (!value_norm) {
+        for (int c = threadIdx.x; c < v_width; c += blockDim.x) {
+            const int g = c / vdim, d = c - g * vdim;
+            v_cache[(tile_row + (size_t)g * block_size) * vdim + d] = from_float<T>(v_src[c] + (v_bias ? v_bias[c] : 0.0f));
+        }
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int g = warp; g < num_kv_heads; g += warps) {
+        const float* head = v_src + (size_t)g * vdim;
+        const float* bias = v_bias ? v_bias + (size_t)g * vdim : nullptr;
+        float squares = 0.0f;
+        for (int d = lane; d < vdim; d += 32) {
+            const float v = head[d] + (bias ? bias[d] : 0.0f);
+            squares = fmaf(v, v, squares);
+        }
+        const float inverse = 1.0f / sqrtf(warp_sum(squares) / (float)vdim + value_eps);
+        T* dst = v_cache + (tile_row + (size_t)g * block_size) * vdim;
+        for (int d = lane; d < vdim; d += 32) dst[d] = from_float<T>((head[d] + (bias ? bias[d] : 0.0f)) * inverse);
+    }
+}
+
+__device__ __forceinline__ float general_dot(const float* __restrict__ q, const float* __restrict__ row, int dim) {
+    float sum = 0.0f;
+    if ((dim & 3) == 0) {
+        for (int d = 0; d < dim; d += 4) {
+            const float4 k = *(const float4*)(row + d);
+            sum = fmaf(q[d], k.x, sum); sum = fmaf(q[d + 1], k.y, sum);
+            sum = fmaf(q[d + 2], k.z, sum); sum = fmaf(q[d + 3], k.w, sum);
+        }
+    } else {
+        for (int d = 0; d < dim; ++d) sum = fmaf(q[d], row[d], sum);
+    }
+    return sum;
+}
+
+__device__ __forceinline__ float general_dot(const float* __restrict__ q, const __nv_bfloat16* __restrict__ row, int dim) {
+    float sum = 0.0f;
+    if ((dim & 7) == 0) {
+        for (int d = 0; d < dim; d += 8) {
+            const uint4 raw = *(const uint4*)(row + d);
+            const __nv_bfloat162* pairs = (const __nv_bfloat162*)&raw;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 k = __bfloat1622float2(pairs[i]);
+                sum = fmaf(q[d + 2 * i], k.x, sum);
+                sum = fmaf(q[d + 2 * i + 1], k.y, sum);
+            }
+        }
+    } else {
+        for (int d = 0; d < dim; ++d) sum = fmaf(q[d], __bfloat162float(row[d]), sum);
+    }
+    return sum;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(GEN_WARPS * 32)
+attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                         const int* __restrict__ block_table, int table_width, const int* __restrict__ positions,
+                         const int* __restrict__ token_seq, T* __restrict__ out, int n_tokens, int num_heads,
+                         int num_kv_heads, int dim, int vdim, int block_size, float scale, int window,
+                         const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ gate,
+                         int gate_stride, int out_stride) {
+    extern __shared__ __align__(16) float general_q[];          // [GEN_WARPS][dim rounded up to 4]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * GEN_WARPS + warp;
+    if (item >= (long long)n_tokens * num_heads) return;        // whole warps leave together
+    const int t = (int)(item / num_heads), head = (int)(item % num_heads);
+    const int kv_head = head / (num_heads / num_kv_heads);
+    const int pos = positions[t];
+    const int* table = block_table + (size_t)token_seq[t] * table_width;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const float slope = r1 ? r1[head] : 0.0f, reach = r1 ? r2[head] : 0.0f;
+
+    float* qs = general_q + (size_t)warp * ((dim + 3) & ~3);
+    const T* q_row = q + ((size_t)t * num_heads + head) * dim;
+    for (int d = lane; d < dim; d += 32) qs[d] = to_float(q_row[d]);
+    __syncwarp();
+
+    float acc[GEN_ACC];
+#pragma unroll
+    for (int i = 0; i < GEN_ACC; ++i) acc[i] = 0.0f;
+    float running_max = -INFINITY, running_sum = 0.0f;
+
+    for (int j0 = lo; j0 <= pos; j0 += 32) {
+        const int j = j0 + lane;
+        const bool valid = j <= pos;
+        size_t row = 0;                                // row of this key in units of one head's vector
+        float score = -INFINITY;
+        if (valid) {
+            const int block = table[j / block_size];
+            row = ((size_t)block * num_kv_heads + kv_head) * block_size + (j % block_size);
+            score = general_dot(qs, k_cache + row * dim, dim) * scale;
+            if (r1) score -= slope * log1pf(reach * (float)(pos - j));
+        }
+        const float new_max = fmaxf(running_max, warp_max(score));
+        const float p = valid ? expf(score - new_max) : 0.0f;
+        const float rescale = expf(running_max - new_max);     // 0 on the first chunk
+        running_sum = running_sum * rescale + warp_sum(p);
+        running_max = new_max;
+#pragma unroll
+        for (int i = 0; i < GEN_ACC; ++i) acc[i] *= rescale;
+        const int count = min(32, pos - j0 + 1);
+        for (int jj = 0; jj < count; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const unsigned long long rj = __shfl_sync(0xffffffffu, (unsigned long long)row, jj);
+            const T* v_row = v_cache + (size_t)rj * vdim;
+#pragma unroll
+            for (int i = 0; i < GEN_ACC; ++i) {
+                const int d = lane + 32 * i;
+                if (d < vdim) acc[i] = fmaf(pj, to_float(v_row[d]), acc[i]);
+            }
+        }
+    }
+    float factor = 1.0f / running_sum;
+    if (gate) factor *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + head]));
+    T* out_row = out + (size_t)t * out_stride + (size_t)head * vdim;
+#pragma unroll
+    for (int i = 0; i < GEN_ACC; ++i) {
+        const int d = lane + 32 * i;
+        if (d < vdim) out_row[d] = from_float<T>(acc[i] * factor);
+    }
+    // columns that pad a row for the projection after it are zero
+    if (head == num_heads - 1)
+        for (int c = num_heads * vdim + lane; c < out_stride; c += 32) out[(size_t)t * out_stride + c] = from_float<T>(0.0f);
+}
+
+}  // namespace skv
+
+using namespace skv;
+
+// `qkv`: float [n_tokens, row_stride], a row holding heads*dim query, kv_heads*dim key and kv_heads*vdim value
+// numbers (whatever follows them is not read).  Biases are float and may be null.
+SKV_EXPORT int skv_qkv_finish(const float* qkv, int row_stride, const float* q_bias, const float* k_bias,
+                              const float* v_bias, const int* positions, const int* token_seq,
+                              const int* block_table, int table_width, void* q_out, void* k_cache, void* v_cache,
+                              int n_tokens, int num_heads, int num_kv_heads, int dim, int vdim, int block_size,
+                              int value_norm, float value_eps, int write_kv, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (num_heads <= 0 || num_kv_heads <= 0 || dim <= 0 || vdim <= 0 || block_size <= 0)
+        return fail("skv_qkv_finish", "head counts, head sizes and block_size must be positive");
+    if (row_stride < (num_heads + num_kv_heads) * dim + num_kv_heads * vdim)
+        return fail("skv_qkv_finish", "a row is shorter than its queries, keys and values");
+    return launch_pdl("skv_qkv_finish", qkv_finish_kernel<skv_t>, dim3(n_tokens), dim3(128), 0, stream, qkv,
+                      row_stride, q_bias, k_bias, v_bias, positions, token_seq, block_table, table_width,
+                      (skv_t*)q_out, (skv_t*)k_cache, (skv_t*)v_cache, num_heads, num_kv_heads, dim, vdim,
+                      block_size, value_norm, value_eps, write_kv);
+}
+
+// `r1`, `r2`: float [num_heads] or both null.  `gate`: float, the gate's logit of (token t, head h) at
+// gate[t * gate_stride + h], or null.  `out` rows are out_stride >= heads * vdim apart; what lies beyond a row's
+// heads is set to zero.
+SKV_EXPORT int skv_attention_general(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                     int table_width, const int* positions, const int* token_seq, void* out,
+                                     int n_tokens, int num_heads, int num_kv_heads, int dim, int vdim, int block_size,
+                                     float scale, int window, const float* r1, const float* r2, const float* gate,
+                                     int gate_stride, int out_stride, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
+        return fail("skv_attention_general", "heads must be a positive multiple of kv heads");
+    if (dim <= 0 || vdim <= 0 || vdim > GEN_MAX_VDIM) return fail("skv_attention_general", "value heads of 1 to 256 numbers are served");
+    if (block_size <= 0 || window < 0) return fail("skv_attention_general", "bad block size or window");
+    if (out_stride < num_heads * vdim) return fail("skv_attention_general", "a row of the output is shorter than its heads");
+    if ((r1 == nullptr) != (r2 == nullptr)) return fail("skv_attention_general", "the distance bias needs both of its numbers per head");
+    const size_t smem = (size_t)GEN_WARPS * ((dim + 3) & ~3) * sizeof(float);
+    if (smem > 48 * 1024) return fail("skv_attention_general", "the key size is too large");
+    const long long items = (long long)n_tokens * num_heads;
+    const long long blocks = (items + GEN_WARPS - 1) / GEN_WARPS;
+    if (blocks > 0x7fffffffLL) return fail("skv_attention_general", "too many tokens in one step");
+    return launch_pdl("skv_attention_general", attention_general_kernel<skv_t>, dim3((unsigned)blocks),
+                      dim3(GEN_WARPS * 32), smem, stream, (const skv_t*)q, (const skv_t*)k_cache,
+                      (const skv_t*)v_cache, block_table, table_width, positions, token_seq, (skv_t*)out, n_tokens,
+                      num_heads, num_kv_heads, dim, vdim, block_size, scale, window, r1, r2, gate, gate_stride, out_stride);
+}

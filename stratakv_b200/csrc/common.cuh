@@ -98,11 +98,29 @@ inline int sm_count() {
 }
 
 // Activations of a gated feed-forward's gate, chosen by the part's spec (ops.ACTIVATIONS has the names).
-enum { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_COUNT = 2 };
+enum { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_RELU2 = 2, ACT_COUNT = 3 };
+// Added to an activation's code where a projection without a gate applies it to what it stores
+// (out = act(a . w^T), the plain feed-forward): the store epilogues look for this bit.
+constexpr int ACT_ON_STORE = 0x100;
 
 // gelu(g) = g/2 * (1 + tanh(sqrt(2/pi) * (g + 0.044715 g^3))), the "tanh" form.
 __device__ __forceinline__ float gelu_tanh(float g) {
     return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+
+// relu(z)^2
+__device__ __forceinline__ float relu_squared(float z) {
+    const float r = fmaxf(z, 0.0f);
+    return r * r;
+}
+
+// What a store epilogue writes for the accumulated value v: v itself, or (ACT_ON_STORE) its activation.
+__device__ __forceinline__ float stored_value(float v, int act) {
+    if (!(act & ACT_ON_STORE)) return v;
+    const int code = act & 0xff;
+    if (code == ACT_RELU2) return relu_squared(v);
+    if (code == ACT_GELU_TANH) return gelu_tanh(v);
+    return v / (1.0f + expf(-v));                     // silu
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -49,6 +49,66 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 }
 
 // ---------------------------------------------------------------------------
+// An embedding that is a sum of tables, in float: x[t, :] = table[ids[t], :]
+//   + pair_table[row, :]      (pair_table given) where row = (previous id * mul_prev + id * mul_cur) mod buckets,
+//                             and row = buckets (the table's last row) for a sequence's first token;
+//   + position_table[p, :] * position_scale     (position_table given), p the token's position.
+// The previous id of a step's first token of a sequence that has run before comes from that sequence's two
+// entries of last_ids (its state: remember_last_ids_kernel writes it after every step): the id of the last token
+// at an even position and of the last at an odd one.  A token at position p reads entry (p - 1) & 1 and a step
+// writes entry (its last position) & 1, so a step that runs twice (the eager run before a graph's capture, then
+// the graph) reads the same id both times.  An id outside the vocabulary or a
+// position beyond the table writes zeros for that term and raises the flag.
+template <typename T>
+__global__ void embed_sum_kernel(const T* __restrict__ table, const T* __restrict__ pair_table,
+                                 const T* __restrict__ position_table, const int* __restrict__ ids,
+                                 const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                 const int* __restrict__ cu_q, const int* __restrict__ slot_ids,
+                                 const int* __restrict__ last_ids, float* __restrict__ out, int hidden, int vocab,
+                                 int buckets, long long mul_prev, long long mul_cur, int max_positions,
+                                 float position_scale, int* __restrict__ flag) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int id = ids[t], pos = positions[t];
+    const bool bad = id < 0 || id >= vocab;
+    const bool beyond = position_table && (pos < 0 || pos >= max_positions);
+    if ((bad || beyond) && threadIdx.x == 0 && flag) atomicOr(flag, bad ? 1 : 8);
+    const T* row = table + (size_t)(bad ? 0 : id) * hidden;
+    const T* pair_row = nullptr;
+    if (pair_table) {
+        long long bucket = buckets;
+        if (pos > 0) {
+            const int seq = token_seq[t];
+            const int previous = t > cu_q[seq] ? ids[t - 1] : last_ids[2 * slot_ids[seq] + ((pos - 1) & 1)];
+            bucket = ((long long)previous * mul_prev + (long long)id * mul_cur) % buckets;
+            if (bucket < 0) bucket += buckets;
+        }
+        pair_row = pair_table + (size_t)bucket * hidden;
+    }
+    const T* position_row = position_table && !beyond ? position_table + (size_t)pos * hidden : nullptr;
+    float* row_out = out + (size_t)t * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = bad ? 0.0f : to_float(row[c]);
+        if (pair_row && !bad) v += to_float(pair_row[c]);
+        if (position_row) v += to_float(position_row[c]) * position_scale;
+        row_out[c] = v;
+    }
+}
+
+// last_ids[slot of sequence s][parity of its position] = the id of the last token that sequence s brought to this step.
+__global__ void remember_last_ids_kernel(const int* __restrict__ ids, const int* __restrict__ positions,
+                                         const int* __restrict__ cu_q, const int* __restrict__ slot_ids,
+                                         int* __restrict__ last_ids, int n_seqs) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n_seqs) return;
+    const int last = cu_q[s + 1] - 1;
+    last_ids[2 * slot_ids[s] + (positions[last] & 1)] = ids[last];
+}
+
+// ---------------------------------------------------------------------------
 // y[r, :] = x[src(r), :] * (1 / sqrt(mean(x^2) + eps)) * gamma, sums in float.
 // The multiplication order is the reference's (src/layers/rmsnorm.cpp:91-93).
 template <typename T>
@@ -267,6 +327,14 @@ __global__ void add_inplace_kernel(float* __restrict__ out, const float* __restr
         out[i] += in[i];
 }
 
+// x[i] *= factor  (a head that scales its logits)
+__global__ void scale_inplace_kernel(float* __restrict__ x, float factor, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] *= factor;
+}
+
 }  // namespace skv
 
 using namespace skv;
@@ -329,6 +397,29 @@ SKV_EXPORT int skv_embed(const void* table, const int* ids, float* out, int n_to
                       (skv_t*)scaled, partials, partial_stride);
 }
 
+// `pair_table` [buckets + 1, hidden] and `position_table` [max_positions, hidden] may be null (that term is left out).
+// `last_ids` holds two ids per sequence slot; it is read here and brought up to date by a second launch.
+SKV_EXPORT int skv_embed_sum(const void* table, const void* pair_table, const void* position_table, const int* ids,
+                             const int* positions, const int* token_seq, const int* cu_q, const int* slot_ids,
+                             int* last_ids, float* out, int n_tokens, int n_seqs, int hidden, int vocab, int buckets,
+                             long long mul_prev, long long mul_cur, int max_positions, float position_scale,
+                             int* flag, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hidden <= 0 || vocab <= 0 || n_seqs <= 0) return fail("skv_embed_sum", "hidden, vocab and the number of sequences must be positive");
+    if (pair_table && (buckets <= 0 || !last_ids || !cu_q || !slot_ids || !token_seq))
+        return fail("skv_embed_sum", "a pair table needs its number of buckets and the sequences' last ids");
+    if (position_table && max_positions <= 0) return fail("skv_embed_sum", "a position table needs its length");
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (int code = launch_pdl("skv_embed_sum", embed_sum_kernel<skv_t>, dim3(n_tokens), dim3(threads), 0, stream,
+                              (const skv_t*)table, (const skv_t*)pair_table, (const skv_t*)position_table, ids,
+                              positions, token_seq, cu_q, slot_ids, (const int*)last_ids, out, hidden, vocab, buckets,
+                              mul_prev, mul_cur, max_positions, position_scale, flag))
+        return code;
+    if (!pair_table) return 0;
+    return launch_pdl("skv_embed_sum", remember_last_ids_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, stream, ids,
+                      positions, cu_q, slot_ids, last_ids, n_seqs);
+}
+
 SKV_EXPORT int skv_rmsnorm(const float* x, const float* gamma, float eps, void* out, const int* rows,
                            int n_rows, int hidden, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
@@ -360,6 +451,14 @@ SKV_EXPORT int skv_rope_kv_write(const float* qkv, const float* cos_sin, const i
     return launch_pdl("skv_rope_kv_write", rope_kv_write_kernel<skv_t>, dim3(n_tokens), dim3(128), 0, stream, qkv,
                       (const float2*)cos_sin, positions, token_seq, block_table, table_width, (skv_t*)q_out,
                       (skv_t*)k_cache, (skv_t*)v_cache, num_heads, num_kv_heads, head_dim, block_size, write_kv);
+}
+
+SKV_EXPORT int skv_scale_inplace(float* x, float factor, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    long long blocks = (n + 255) / 256;
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+    return launch_pdl("skv_scale_inplace", scale_inplace_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, factor,
+                      (size_t)n);
 }
 
 SKV_EXPORT int skv_add_inplace(float* out, const float* in, long long n, cudaStream_t stream) {

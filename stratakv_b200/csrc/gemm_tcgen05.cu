@@ -165,6 +165,7 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) 
 // 256-column tile took longer than the tile's main loop (2,048 x 11,264 x 2,048: 76.7 us against 63.8 us).  Past
 // z = -88 the exponential overflows to infinity and the quotient is -0, the right limit.
 __device__ __forceinline__ float gate_activation(float g, int act) {
+    if (act == ACT_RELU2) return relu_squared(g);
     const float z = act == ACT_GELU_TANH ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
     return __fdividef(g, 1.0f + __expf(-z));
 }
@@ -241,7 +242,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, in
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const __nv_bfloat162 pair = __floats2bfloat162_rn(
-                                __uint_as_float(v[8 * piece + 2 * e]), __uint_as_float(v[8 * piece + 2 * e + 1]));
+                                stored_value(__uint_as_float(v[8 * piece + 2 * e]), act),
+                                stored_value(__uint_as_float(v[8 * piece + 2 * e + 1]), act));
                             packed[e] = *(const uint32_t*)&pair;
                         }
                         slab_write(slab, lane, sub * 4 + piece, make_uint4(packed[0], packed[1], packed[2], packed[3]));
@@ -301,14 +303,14 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, in
                         uint32_t packed[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * e]),
-                                                                              __uint_as_float(v[j + 2 * e + 1]));
+                            const __nv_bfloat162 pair = __floats2bfloat162_rn(stored_value(__uint_as_float(v[j + 2 * e]), act),
+                                                                              stored_value(__uint_as_float(v[j + 2 * e + 1]), act));
                             packed[e] = *(const uint32_t*)&pair;
                         }
                         *(uint4*)(dst + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     }
                 } else {
-                    for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                    for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(stored_value(__uint_as_float(v[j]), act));
                 }
             } else {
                 float* dst = (float*)out + (size_t)m * N + n;
@@ -975,7 +977,7 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
                 if (mode == TC_MODE_STORE) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        if (c + j < M) ((__nv_bfloat16*)out)[(size_t)(c + j) * N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                        if (c + j < M) ((__nv_bfloat16*)out)[(size_t)(c + j) * N + n] = __float2bfloat16_rn(stored_value(__uint_as_float(v[j]), act));
                 } else if (mode == TC_MODE_STORE_F32) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)

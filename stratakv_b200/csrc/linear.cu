@@ -24,9 +24,13 @@
 namespace skv {
 
 enum { MODE_STORE = 0, MODE_STORE_F32 = 1, MODE_ADD_F32 = 2, MODE_GATED = 3 };
+// What callers name besides: out = act(a . w^T) in the compute dtype.  Inside the library it is MODE_STORE
+// with ACT_ON_STORE added to the activation's code.
+constexpr int MODE_STORE_ACT = 5;
 
 __device__ __forceinline__ float activate(float g, int act) {
     if (act == ACT_GELU_TANH) return gelu_tanh(g);
+    if (act == ACT_RELU2) return relu_squared(g);
     // silu(g) = g * sigmoid(g); the two-branch sigmoid of the reference's CPU
     // block (src/models/transformer_block.cpp:315-323) avoids overflow of exp.
     const float sig = g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : expf(g) / (1.0f + expf(g));
@@ -34,10 +38,10 @@ __device__ __forceinline__ float activate(float g, int act) {
 }
 
 template <typename T>
-__device__ __forceinline__ void epilogue_store(void* out, int mode, int M, int N, int m, int n, float v) {
+__device__ __forceinline__ void epilogue_store(void* out, int mode, int M, int N, int m, int n, float v, int act) {
     if (m >= M || n >= N) return;
     const size_t at = (size_t)m * N + n;
-    if (mode == MODE_STORE) ((T*)out)[at] = from_float<T>(v);
+    if (mode == MODE_STORE) ((T*)out)[at] = from_float<T>(stored_value(v, act));
     else if (mode == MODE_STORE_F32) ((float*)out)[at] = v;
     else ((float*)out)[at] += v;
 }
@@ -102,7 +106,7 @@ linear_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, void
             }
         } else {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) epilogue_store<float>(out, mode, M, N, m, n0 + cols[c], acc[i][c]);
+            for (int c = 0; c < 4; ++c) epilogue_store<float>(out, mode, M, N, m, n0 + cols[c], acc[i][c], act);
         }
     }
 }
@@ -330,7 +334,7 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
     } else {
         for (int idx = threadIdx.x; idx < 16 * COLS; idx += blockDim.x) {
             const int r = idx & 15, m = idx >> 4;
-            epilogue_store<__nv_bfloat16>(out, mode, M, N, m0 + m, n0 + r, red[(size_t)r * PITCH + m]);
+            epilogue_store<__nv_bfloat16>(out, mode, M, N, m0 + m, n0 + r, red[(size_t)r * PITCH + m], act);
         }
     }
 }
@@ -409,7 +413,8 @@ static int check_linear(int M, int N, int K, int mode, int act) {
     if (mode < 0 || mode > 3) return fail("skv_linear", "unknown epilogue mode");
     if (mode == MODE_GATED && N % 16 != 0)
         return fail("skv_linear", "a gated weight must have a multiple of 16 rows (gate/up tiles of 8)");
-    if (act < 0 || act >= ACT_COUNT) return fail("skv_linear", "unknown activation");
+    if ((act & 0xff) >= ACT_COUNT || (act & ~(0xff | ACT_ON_STORE)) || ((act & ACT_ON_STORE) && mode != MODE_STORE))
+        return fail("skv_linear", "unknown activation");
     (void)M;
     return 0;
 }
@@ -423,6 +428,7 @@ SKV_EXPORT int skv_linear(const void* a, const void* w, void* out, int M, int N,
                           int* flag, void* scaled_out, const float* gamma_next, float* partials, int partial_stride,
                           float* row_scale_out, float eps_next, unsigned int* counter, cudaStream_t stream) {
     if (M <= 0) return 0;
+    if (mode == MODE_STORE_ACT) { mode = MODE_STORE; act |= ACT_ON_STORE; }
     if (int code = check_linear(M, N, K, mode, act)) return code;
     NormArgs norm = {};
     if (scaled_out) {
@@ -447,6 +453,7 @@ SKV_EXPORT int skv_linear_normed(const void* a, const float* row_scale, const fl
                                  int partial_stride, float eps, const int* rows, const void* w, void* out, int M,
                                  int N, int K, int mode, int act, cudaStream_t stream) {
     if (M <= 0) return 0;
+    if (mode == MODE_STORE_ACT) { mode = MODE_STORE; act |= ACT_ON_STORE; }
     if (int code = check_linear(M, N, K, mode, act)) return code;
     if (!row_scale && (!partials || n_partials <= 0 || partial_stride < n_partials))
         return fail("skv_linear_normed", "the rows' factors, or their partial sums of squares, are needed");

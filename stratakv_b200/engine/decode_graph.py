@@ -110,7 +110,7 @@ class DecodeGraph:
         if live < b:
             pos[live:] = 0
             after[live:] = 1
-            slot_ids[live:] = 0
+            slot_ids[live:] = cache.spare_slot
         for g, group in enumerate(cache.groups):
             table = self._np(("table", g)).reshape(b, self.width)
             for row in range(b):

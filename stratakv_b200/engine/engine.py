@@ -71,6 +71,9 @@ class Engine:
         self.config = config
         # most positions a sequence may reach: the engine's setting, else the model's own limit, else none
         self.max_context = config.max_context or spec.max_positions or 0
+        if spec.positions_are_tabled and spec.max_positions:
+            # learned positions end where their table ends, whatever the engine is told
+            self.max_context = min(self.max_context or spec.max_positions, spec.max_positions)
         if kernel_loader is None:
             self.device = _ops.require_cuda(config.device)
             kernel_loader = lambda dtype, head_dim: _ops.kernels_for(dtype, head_dim, verbose=verbose)
@@ -418,7 +421,8 @@ class _Chooser:
 
 FLAG_MEANINGS = {1: "a token id outside the vocabulary reached the embedding",
                  2: "non-finite logits",
-                 4: "a wait inside a kernel timed out (its result is not valid)"}
+                 4: "a wait inside a kernel timed out (its result is not valid)",
+                 8: "a position beyond the table of learned positions reached the embedding"}
 
 
 def describe_flags(word: int) -> str:

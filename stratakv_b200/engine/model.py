@@ -55,13 +55,22 @@ def cache_requests(spec: ModelSpec) -> List[CacheRequest]:
     for index, request in enumerate(requests):
         if request is None:
             raise ValueError(f"cache entry {index} is read but no run writes it")
+    embedding_state = embedding_cache_request(spec)
+    if embedding_state is not None:
+        requests.append(embedding_state)           # the entry after the layers': Model tells the part its index
     return requests
+
+
+def embedding_cache_request(spec: ModelSpec) -> Optional[CacheRequest]:
+    """Per-sequence state that the embedding keeps (the token before, for an embedding of token pairs), or None."""
+    ask = getattr(part_class("embedding", spec.embedding.kind), "cache_request", None)
+    return ask(spec.embedding) if ask is not None else None
 
 
 def default_head_dim(spec: ModelSpec) -> int:
     for layer in spec.layers:
         head_dim = getattr(layer.mixer, "head_dim", None)
-        if head_dim:
+        if head_dim and head_dim % 16 == 0 and head_dim <= 256:      # (the sizes a library can be built for)
             return head_dim
     return 64       # no part needs a head size: any build of the library will do
 
@@ -74,7 +83,9 @@ class Model:
         self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, runtime)
         self.embedding = part_class("embedding", spec.embedding.kind)(spec.embedding, runtime)
         self.head = part_class("head", spec.head.kind)(spec.head, runtime)
-        # Raised by kernels: bit 0 = token id outside the vocabulary.
+        if embedding_cache_request(spec) is not None:
+            self.embedding.state_entry = spec.num_cache_entries()
+        # Raised by kernels: bit 0 = token id outside the vocabulary, bit 3 = position beyond a table.
         self.flags = torch.zeros(1, dtype=torch.int32, device=runtime.device)
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:

@@ -1,2 +1,3 @@
 """Architectures.  Importing this package registers every one of them."""
 from . import llama  # noqa: F401
+from . import zepavik  # noqa: F401

@@ -16,8 +16,9 @@ from .residual import COLUMNS_PER_PARTIAL, KERNEL_FOLD_ROWS, NormedRows
 
 MODE_STORE, MODE_STORE_F32, MODE_ADD_F32, MODE_GATED = 0, 1, 2, 3
 MODE_QKV_ROPE = 4          # (linear_qkv_rope's own epilogue; named for Kernels.linear_form)
-# activations of a gated feed-forward's gate that every projection kernel implements (csrc/common.cuh)
-ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1}
+MODE_ACT = 5               # out = act(a . w^T) in the compute dtype: the first projection of a feed-forward without a gate
+# activations that every projection kernel implements, on a gate or on what it stores (csrc/common.cuh)
+ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1, "relu2": 2, "relu_squared": 2}
 _DTYPE_NAMES = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
 
 
@@ -181,7 +182,7 @@ class Kernels:
         if w.shape[1] != K:
             raise KernelError(f"linear: inner sizes differ ({K} and {w.shape[1]})")
         out_cols = N // 2 if mode == MODE_GATED else N
-        out_dtype = self.dtype if mode in (MODE_STORE, MODE_GATED) else torch.float32
+        out_dtype = self.dtype if mode in (MODE_STORE, MODE_GATED, MODE_ACT) else torch.float32
         self._want(out, out_dtype, "out")
         if tuple(out.shape) != (M, out_cols):
             raise KernelError(f"linear: out must be [{M}, {out_cols}], got {list(out.shape)}")
@@ -361,6 +362,100 @@ class Kernels:
             _ptr(qkv), _ptr(cos_sin), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
             _ptr(ctx_after), _ptr(out), n, num_heads, num_kv_heads, head_dim, block_size, ctypes.c_float(scale),
             window, splits, int(bool(write_kv)), _stream()), "attention_decode_fused")
+
+    def embed_sum(self, table, ids, out, positions, token_seq, cu_q, slot_ids, flag=None, pair_table=None,
+                  last_ids=None, mul_prev: int = 0, mul_cur: int = 0, position_table=None,
+                  position_scale: float = 1.0):
+        """out[t, :] = table[ids[t]] + pair_table[bucket(previous id, ids[t])] + position_table[positions[t]] *
+        position_scale, summed in float32; either of the two further tables may be None.  ``pair_table`` has one row
+        per bucket and a last row for a sequence's first token; ``last_ids`` (int32, two per sequence slot: by the parity of the
+        position) holds the last ids each sequence brought to its steps before and is brought up to date."""
+        self._want(table, self.dtype, "table"); self._want(ids, torch.int32, "ids")
+        self._want(out, torch.float32, "out"); self._want(positions, torch.int32, "positions")
+        self._want(token_seq, torch.int32, "token_seq"); self._want(cu_q, torch.int32, "cu_q")
+        self._want(slot_ids, torch.int32, "slot_ids")
+        n, hidden = out.shape
+        n_seqs = slot_ids.numel()
+        if table.shape[1] != hidden or ids.numel() != n or positions.numel() != n or cu_q.numel() != n_seqs + 1:
+            raise KernelError("embed_sum: shapes do not agree")
+        buckets = 0
+        if pair_table is not None:
+            self._want(pair_table, self.dtype, "pair_table"); self._want(last_ids, torch.int32, "last_ids")
+            buckets = pair_table.shape[0] - 1
+            if pair_table.shape[1] != hidden or buckets < 1:
+                raise KernelError("embed_sum: the pair table must be [buckets + 1, hidden]")
+        max_positions = 0
+        if position_table is not None:
+            self._want(position_table, self.dtype, "position_table")
+            max_positions = position_table.shape[0]
+            if position_table.shape[1] != hidden:
+                raise KernelError("embed_sum: the position table must be [positions, hidden]")
+        self._check(self.lib.skv_embed_sum(
+            _ptr(table), _ptr(pair_table), _ptr(position_table), _ptr(ids), _ptr(positions), _ptr(token_seq), _ptr(cu_q),
+            _ptr(slot_ids), _ptr(last_ids), _ptr(out), n, n_seqs, hidden, table.shape[0], buckets,
+            ctypes.c_longlong(mul_prev), ctypes.c_longlong(mul_cur), max_positions, ctypes.c_float(position_scale),
+            _ptr(flag), _stream()), "embed_sum")
+        if pair_table is not None:
+            Kernels.launches += 1              # (the second launch that remembers the last ids)
+
+    def qkv_finish(self, qkv, q_out, k_cache, v_cache, positions, token_seq, block_table, num_heads: int,
+                   num_kv_heads: int, dim: int, vdim: int, block_size: int, q_bias=None, k_bias=None, v_bias=None,
+                   value_norm_eps=None, write_kv: bool = True):
+        """From float32 rows ``[q | k | v | ...]`` of a fused projection: biases added, each value head divided by
+        its root mean square (``value_norm_eps`` not None), queries to ``q_out`` and keys and values to the cache
+        in the compute dtype.  Any head sizes; keys ``dim`` and values ``vdim`` wide."""
+        self._want(qkv, torch.float32, "qkv"); self._want(q_out, self.dtype, "q_out")
+        self._want(positions, torch.int32, "positions"); self._want(token_seq, torch.int32, "token_seq")
+        self._want(block_table, torch.int32, "block_table")
+        self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
+        for name, bias, width in (("q_bias", q_bias, num_heads * dim), ("k_bias", k_bias, num_kv_heads * dim),
+                                  ("v_bias", v_bias, num_kv_heads * vdim)):
+            if bias is not None:
+                self._want(bias, torch.float32, name)
+                if bias.numel() != width:
+                    raise KernelError(f"qkv_finish: {name} must hold {width} numbers")
+        n = qkv.shape[0]
+        if tuple(q_out.shape) != (n, num_heads * dim) or positions.numel() != n or token_seq.numel() != n:
+            raise KernelError("qkv_finish: one query row, one position and one sequence index per token is needed")
+        if (tuple(k_cache.shape[1:]) != (num_kv_heads, block_size, dim)
+                or tuple(v_cache.shape[1:]) != (num_kv_heads, block_size, vdim)):
+            raise KernelError("qkv_finish: the cache must be [blocks, kv_heads, block_size, dim] and [.., vdim]")
+        self._check(self.lib.skv_qkv_finish(
+            _ptr(qkv), qkv.shape[1], _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), _ptr(positions), _ptr(token_seq),
+            _ptr(block_table), block_table.shape[1], _ptr(q_out), _ptr(k_cache), _ptr(v_cache), n, num_heads,
+            num_kv_heads, dim, vdim, block_size, int(value_norm_eps is not None),
+            ctypes.c_float(value_norm_eps or 0.0), int(bool(write_kv)), _stream()), "qkv_finish")
+
+    def attention_general(self, q, k_cache, v_cache, block_table, positions, token_seq, out, num_heads: int,
+                          num_kv_heads: int, dim: int, vdim: int, block_size: int, scale: float, window: int = 0,
+                          r1=None, r2=None, gate=None, gate_stride: int = 0):
+        """Attention with run-time head sizes (keys ``dim``, values ``vdim``), a warp per (token, head), float math.
+        ``r1``, ``r2`` (float32 per head): ``r1 * ln(1 + r2 * distance)`` is taken off each score.  ``gate``
+        (float32, the logit of token t and head h at ``[t * gate_stride + h]``): the head's output times its sigmoid.
+        ``out`` may be wider than ``heads * vdim``; the further columns are set to zero."""
+        self._want(q, self.dtype, "q"); self._want(out, self.dtype, "out")
+        self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
+        self._want(block_table, torch.int32, "block_table")
+        self._want(positions, torch.int32, "positions"); self._want(token_seq, torch.int32, "token_seq")
+        for name, value in (("r1", r1), ("r2", r2)):
+            if value is not None:
+                self._want(value, torch.float32, name)
+                if value.numel() != num_heads:
+                    raise KernelError(f"attention_general: {name} must hold one number per head")
+        if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda or gate_stride < num_heads):
+            raise KernelError("attention_general: the gate must be float32 on the GPU, a row at least heads wide")
+        n = q.shape[0]
+        if tuple(q.shape) != (n, num_heads * dim) or out.shape[0] != n or out.shape[1] < num_heads * vdim:
+            raise KernelError("attention_general: q must be [tokens, heads * dim] and out [tokens, heads * vdim or wider]")
+        self._check(self.lib.skv_attention_general(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(positions),
+            _ptr(token_seq), _ptr(out), n, num_heads, num_kv_heads, dim, vdim, block_size, ctypes.c_float(scale),
+            window, _ptr(r1), _ptr(r2), _ptr(gate), gate_stride, out.shape[1], _stream()), "attention_general")
+
+    def scale_inplace(self, x, factor: float):
+        self._want(x, torch.float32, "x")
+        self._check(self.lib.skv_scale_inplace(_ptr(x), ctypes.c_float(factor), ctypes.c_longlong(x.numel()), _stream()),
+                    "scale_inplace")
 
     def add_inplace(self, out, other):
         self._want(out, torch.float32, "out"); self._want(other, torch.float32, "other")

@@ -7,6 +7,12 @@ sum of values in float; ``x += ctx.Wo^T`` (``src/layers/attention.cpp:153-342``,
 ``src/models/transformer_block.cpp:301-309``).  The three projections are one
 matrix ``[q | k | v]`` here, and the residual sum is the epilogue of the output
 projection.
+
+A spec may switch on further mechanisms (``parts/spec.py::AttentionSpec``): biases on the projections, values
+of another width than keys, an RMS norm on every value head before it is cached, a bias on the scores by the
+logarithm of the distance, and a gate per head on the output.  Such a mixer projects ``[q | k | v | gate]`` at
+once, finishes the rows in ``qkv_finish`` (biases, value norm, cache write) and attends with the kernels
+that carry the bias and the gate (``csrc/attention_general.cu``).
 """
 from __future__ import annotations
 
@@ -52,20 +58,40 @@ def wants_more_pieces(n_seqs: int, blocks_per_seq: int, max_ctx: int, cluster_sp
 
 class PagedAttention(Mixer):
     graph_safe = True
-    folds_norm = True
+
+    @property
+    def folds_norm(self):
+        return not self.spec.extended
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         if spec.num_heads % spec.num_kv_heads != 0:
             raise ValueError("attention: heads must be a multiple of kv heads")
+        self.q_dim = spec.num_heads * spec.head_dim
+        self.kv_dim = spec.num_kv_heads * spec.head_dim
+        self.v_dim = spec.num_kv_heads * spec.value_dim
+        self.ctx_dim = spec.num_heads * spec.value_dim
+        if spec.extended:
+            if spec.position is not None:
+                raise ValueError("attention: the extended mechanisms are built without a rotation")
+            if spec.value_dim > 256:
+                raise ValueError(f"attention: value heads of {spec.value_dim} numbers are not supported (at most 256)")
+            if runtime.dtype == torch.bfloat16 and spec.hidden_size % 8 != 0:
+                raise ValueError(f"attention: hidden size {spec.hidden_size} is not supported in bfloat16 "
+                                 "(rows of 16 bytes are needed: a multiple of 8); float32 takes any size")
+            # the attention output's rows, padded so that the output projection reads whole 16 bytes
+            self.ctx_width = -(-self.ctx_dim // 8) * 8
+            gate_rows = spec.num_heads if spec.gate_weight else 0
+            self.gate_offset = self.q_dim + self.kv_dim + self.v_dim
+            self.fused_width = -(-(self.gate_offset + gate_rows) // 8) * 8
+            self.position = None
+            return
         if spec.head_dim % 16 != 0:
             raise ValueError(f"attention: head size {spec.head_dim} is not supported "
                              "(the kernels take multiples of 16)")
         if runtime.dtype == torch.bfloat16 and spec.hidden_size % 8 != 0:
             raise ValueError(f"attention: hidden size {spec.hidden_size} is not supported in bfloat16 "
                              "(rows of 16 bytes are needed: a multiple of 8); float32 takes any size")
-        self.q_dim = spec.num_heads * spec.head_dim
-        self.kv_dim = spec.num_kv_heads * spec.head_dim
         position_spec = spec.position
         kind = position_spec.kind if position_spec is not None else "none"
         self.position = part_class("position", kind)(position_spec, runtime)
@@ -73,24 +99,71 @@ class PagedAttention(Mixer):
     @classmethod
     def expected_tensors(cls, spec):
         q_dim, kv_dim = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
-        return {spec.q_weight: TensorRequest((q_dim, spec.hidden_size)),
-                spec.k_weight: TensorRequest((kv_dim, spec.hidden_size)),
-                spec.v_weight: TensorRequest((kv_dim, spec.hidden_size)),
-                spec.o_weight: TensorRequest((spec.hidden_size, q_dim))}
+        v_dim, ctx_dim = spec.num_kv_heads * spec.value_dim, spec.num_heads * spec.value_dim
+        wanted = {spec.q_weight: TensorRequest((q_dim, spec.hidden_size)),
+                  spec.k_weight: TensorRequest((kv_dim, spec.hidden_size)),
+                  spec.v_weight: TensorRequest((v_dim, spec.hidden_size)),
+                  spec.o_weight: TensorRequest((spec.hidden_size, ctx_dim))}
+        for name, width in ((spec.q_bias, q_dim), (spec.k_bias, kv_dim), (spec.v_bias, v_dim)):
+            if name:
+                wanted[name] = TensorRequest((width,))
+        if spec.distance_bias:
+            wanted[spec.distance_bias.r1] = TensorRequest((spec.num_heads,), "positive")
+            wanted[spec.distance_bias.r2] = TensorRequest((spec.num_heads,), "positive")
+        if spec.gate_weight:
+            wanted[spec.gate_weight] = TensorRequest((spec.num_heads, spec.hidden_size))
+        return wanted
 
     @classmethod
     def cache_request(cls, spec):
         kind = "kv_window" if spec.window > 0 else "kv"
-        return CacheRequest(kind, spec.num_kv_heads, spec.head_dim, spec.window)
+        v_head_dim = spec.v_head_dim if spec.v_head_dim != spec.head_dim else 0
+        return CacheRequest(kind, spec.num_kv_heads, spec.head_dim, spec.window, v_head_dim=v_head_dim)
 
     def bind(self, tensors):
         s = self.spec
-        parts = [self.rt.upload(tensors[name]) for name in (s.q_weight, s.k_weight, s.v_weight)]
+        names = [s.q_weight, s.k_weight, s.v_weight] + ([s.gate_weight] if s.extended and s.gate_weight else [])
+        parts = [self.rt.upload(tensors[name]) for name in names]
+        if s.extended:
+            rows = sum(part.shape[0] for part in parts)
+            if rows < self.fused_width:            # (zero rows: what they produce is never read)
+                parts.append(parts[0].new_zeros(self.fused_width - rows, s.hidden_size))
         self.w_qkv = torch.cat(parts, dim=0).contiguous()
         del parts
         self.w_o = self.rt.upload(tensors[s.o_weight])
+        if not s.extended:
+            return
+        if self.ctx_width != self.ctx_dim:
+            self.w_o = torch.cat([self.w_o, self.w_o.new_zeros(s.hidden_size, self.ctx_width - self.ctx_dim)], dim=1).contiguous()
+        as_float = lambda name: self.rt.upload(tensors[name], torch.float32) if name else None
+        self.q_bias, self.k_bias, self.v_bias = as_float(s.q_bias), as_float(s.k_bias), as_float(s.v_bias)
+        self.r1 = as_float(s.distance_bias.r1) if s.distance_bias else None
+        self.r2 = as_float(s.distance_bias.r2) if s.distance_bias else None
+
+    def _forward_extended(self, step, h, x, cache_entry, writes_cache=True):
+        """The mixer with any of the further mechanisms: one projection for queries, keys, values and the gates'
+        logits (float32), ``qkv_finish``, attention with the bias and the gate, output projection."""
+        s, rt = self.spec, self.rt
+        ops = rt.kernels()
+        n = h.shape[0]
+        fused = rt.workspace.get("qkv", (n, self.fused_width), torch.float32)
+        ops.linear(h, self.w_qkv, fused, _ops.MODE_STORE_F32)
+        q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
+        k_cache, v_cache = step.cache.entry_kv(cache_entry)
+        table = step.block_tables[step.cache.entry_group_index(cache_entry)]
+        ops.qkv_finish(fused, q, k_cache, v_cache, step.positions, step.token_seq, table, s.num_heads,
+                       s.num_kv_heads, s.head_dim, s.value_dim, step.cache.block_size, self.q_bias, self.k_bias,
+                       self.v_bias, s.value_norm_eps, writes_cache)
+        ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
+        gate = fused[:, self.gate_offset:] if s.gate_weight else None
+        ops.attention_general(q, k_cache, v_cache, table, step.positions, step.token_seq, ctx, s.num_heads,
+                              s.num_kv_heads, s.head_dim, s.value_dim, step.cache.block_size, s.scale, s.window,
+                              self.r1, self.r2, gate, self.fused_width)
+        ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
 
     def forward(self, step, h, x, cache_entry, writes_cache=True):
+        if self.spec.extended:
+            return self._forward_extended(step, h, x, cache_entry, writes_cache)
         s, rt = self.spec, self.rt
         ops = rt.kernels(s.head_dim)
         n = h.shape[0]

@@ -22,7 +22,8 @@ import torch
 @dataclass(frozen=True)
 class TensorRequest:
     """A checkpoint tensor a part needs.  ``init`` tells the random-weights mode
-    how to fill it: ``normal`` is N(0, std), ``around_one`` is 1 + N(0, std)."""
+    how to fill it: ``normal`` is N(0, std), ``around_one`` is 1 + N(0, std), ``positive`` is
+    0.05 + |N(0, 0.5)|."""
     shape: Tuple[int, ...]
     init: str = "normal"
 

@@ -1,8 +1,8 @@
 """Arrangements: how a layer's norms, mixer and feed-forward are strung together.
 
 ``pre_norm`` is the Llama block, ``x += mixer(norm(x)); x += ffn(norm(x))``
-(``src/models/transformer_block.cpp:301-331``).  Another arrangement is one more
-function registered under its name.
+(``src/models/transformer_block.cpp:301-331``); ``parallel`` feeds one norm's output to
+both branches.  Another arrangement is one more function registered under its name.
 """
 from __future__ import annotations
 
@@ -66,4 +66,21 @@ def pre_norm(layer: Layer, step, x, entry) -> None:
         stats.invalidate()
 
 
+def parallel(layer: Layer, step, x, entry) -> None:
+    """``h = norm(x); x += mixer(h) + ffn(h)``: one norm, and both branches read its output.  A layer
+    without a feed-forward is ``x += mixer(norm(x))``."""
+    if layer.mixer_norm is None or layer.mixer is None:
+        raise ValueError("the parallel arrangement needs a norm and a mixer")
+    stats = step.residual_stats
+    if stats is not None:
+        stats.expect(None)                  # (both branches add to the stream: neither leaves the next norm's sums)
+    h = layer.mixer_norm.forward(x)
+    layer.mixer.forward(step, h, x, entry.cache, entry.writes_cache)
+    if layer.ffn is not None:
+        layer.ffn.forward(step, h, x)
+    if stats is not None:
+        stats.invalidate()
+
+
 register_arrangement("pre_norm", pre_norm)
+register_arrangement("parallel", parallel)

@@ -67,4 +67,43 @@ class GatedMlp(FeedForward):
         ops.linear(z, self.w_down, x, _ops.MODE_ADD_F32, stats=getattr(step, "residual_stats", None))
 
 
+class Mlp(FeedForward):
+    """A feed-forward without a gate: ``x += down(act(up(h)))``.  The activation is the epilogue of the up
+    projection (``ops.MODE_ACT``), the residual sum that of the down projection."""
+    graph_safe = True
+    folds_norm = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        if spec.activation not in _ops.ACTIVATIONS:
+            raise ValueError(f"feed-forward: activation '{spec.activation}' is not supported")
+        if runtime.dtype == torch.bfloat16 and spec.hidden_size % 8 != 0:
+            raise ValueError(f"feed-forward: hidden size {spec.hidden_size} is not supported in bfloat16 "
+                             "(rows of 16 bytes are needed: a multiple of 8); float32 takes any size")
+        self.padded = -(-spec.intermediate_size // 8) * 8      # rows of whole 16 bytes for the down projection
+
+    @classmethod
+    def expected_tensors(cls, spec):
+        return {spec.up_weight: TensorRequest((spec.intermediate_size, spec.hidden_size)),
+                spec.down_weight: TensorRequest((spec.hidden_size, spec.intermediate_size))}
+
+    def bind(self, tensors):
+        s = self.spec
+        up = self.rt.upload(tensors[s.up_weight])
+        down = self.rt.upload(tensors[s.down_weight])
+        if self.padded != s.intermediate_size:
+            # zero rows of up give act(0) = 0 for every activation here and meet zero columns of down
+            up = torch.cat([up, up.new_zeros(self.padded - s.intermediate_size, s.hidden_size)], dim=0)
+            down = torch.cat([down, down.new_zeros(s.hidden_size, self.padded - s.intermediate_size)], dim=1)
+        self.w_up, self.w_down = up.contiguous(), down.contiguous()
+
+    def forward(self, step, h, x):
+        s, rt = self.spec, self.rt
+        ops = rt.kernels()
+        z = rt.workspace.get("ffn_hidden", (h.shape[0], self.padded), rt.dtype)
+        ops.linear(h, self.w_up, z, _ops.MODE_ACT, s.activation)
+        ops.linear(z, self.w_down, x, _ops.MODE_ADD_F32, stats=getattr(step, "residual_stats", None))
+
+
 register_ffn("gated_mlp", GatedMlp)
+register_ffn("mlp", Mlp)

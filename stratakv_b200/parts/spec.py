@@ -31,8 +31,22 @@ class RopeSpec:
 
 
 @dataclass(frozen=True)
+class DistanceBiasSpec:
+    """A bias on attention scores that grows with the logarithm of the distance: query i and key j score
+    ``(q.k) * scale - r1[h] * ln(1 + r2[h] * (i - j))`` with two learned numbers per head."""
+    r1: str                          # tensor names, each [num_heads]
+    r2: str
+    kind: str = "log_distance"
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
-    """Causal grouped-query attention over a paged cache (``src/layers/attention.cpp:153-342``)."""
+    """Causal grouped-query attention over a paged cache (``src/layers/attention.cpp:153-342``).
+
+    The fields after ``window`` are mechanisms that a design may add, each off by default: a value head
+    size of its own (``v_head_dim``), biases on the three projections, an RMS norm without weight on every
+    value head before it is cached (``value_norm_eps``), a bias on the scores by distance, and a gate per
+    head on the attention output, ``sigmoid(h . gate_weight[head])``, read from the mixer's own input."""
     hidden_size: int
     num_heads: int
     num_kv_heads: int
@@ -45,6 +59,23 @@ class AttentionSpec:
     o_weight: str
     window: int = 0                  # 0: every earlier key; w > 0: the last w keys only
     kind: str = "attention"
+    v_head_dim: int = 0              # 0: values as wide as keys
+    q_bias: Optional[str] = None     # tensor names
+    k_bias: Optional[str] = None
+    v_bias: Optional[str] = None
+    value_norm_eps: Optional[float] = None
+    distance_bias: Optional[DistanceBiasSpec] = None
+    gate_weight: Optional[str] = None     # [num_heads, hidden_size]
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
+
+    @property
+    def extended(self) -> bool:
+        """True if any mechanism beyond rotated, unbiased queries, keys and values of one width is in use."""
+        return bool(self.v_head_dim and self.v_head_dim != self.head_dim or self.q_bias or self.k_bias
+                    or self.v_bias or self.value_norm_eps is not None or self.distance_bias or self.gate_weight)
 
 
 @dataclass(frozen=True)
@@ -60,11 +91,24 @@ class GatedMlpSpec:
 
 
 @dataclass(frozen=True)
+class MlpSpec:
+    """A feed-forward without a gate: ``down(act(up(x)))``."""
+    hidden_size: int
+    intermediate_size: int
+    activation: str                  # "relu2" (the square of relu), "gelu_tanh", "silu"
+    up_weight: str
+    down_weight: str
+    kind: str = "mlp"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: which norm, mixer and feed-forward, and how they are arranged.
 
     ``pre_norm``: ``x += mixer(norm1(x)); x += ffn(norm2(x))``
     (``src/models/transformer_block.cpp:301-331``).
+    ``parallel``: ``h = norm1(x); x += mixer(h) + ffn(h)``: one norm (``mixer_norm``), both branches read its
+    output; ``ffn`` may be ``None``.
 
     The four named places are what that arrangement uses; another arrangement may leave
     some of them ``None`` (a block without a feed-forward, one norm for two branches) and
@@ -103,13 +147,44 @@ class EmbeddingSpec:
 
 
 @dataclass(frozen=True)
+class HashedPairSpec:
+    """A second embedding table indexed by a hash of two neighbouring tokens: row
+    ``(previous * mul_prev + current * mul_cur) mod buckets``; a sequence's first token reads row ``buckets``,
+    the table's last."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    weight: str                      # [buckets + 1, hidden_size]
+
+
+@dataclass(frozen=True)
+class LearnedPositionSpec:
+    """A learned vector per position, added to the embedding times ``scale``."""
+    max_positions: int
+    weight: str                      # [max_positions, hidden_size]
+    scale: float = 1.0
+
+
+@dataclass(frozen=True)
+class SummedEmbeddingSpec:
+    """``x = table[token] (+ pair table row) (+ position vector)``, summed in float."""
+    vocab_size: int
+    hidden_size: int
+    weight: str
+    pair: Optional[HashedPairSpec] = None
+    positions: Optional[LearnedPositionSpec] = None
+    kind: str = "summed_embedding"
+
+
+@dataclass(frozen=True)
 class HeadSpec:
-    """Final norm on the wanted rows, then ``logits = y . W^T`` (``src/generation/generator.cpp:773-774``).
-    ``weight`` may be the embedding table's name (tied)."""
+    """Final norm on the wanted rows, then ``logits = y . W^T`` (``src/generation/generator.cpp:773-774``)
+    times ``logit_scale``.  ``weight`` may be the embedding table's name (tied)."""
     vocab_size: int
     hidden_size: int
     weight: str
     kind: str = "linear_head"
+    logit_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -124,6 +199,9 @@ class ModelSpec:
     head: HeadSpec
     stop_token_ids: Tuple[int, ...] = ()
     max_positions: int = 0
+    # True if a table holds the positions (learned vectors): no sequence may pass ``max_positions`` then,
+    # whatever the engine is told.
+    positions_are_tabled: bool = False
     # Tensor names a checkpoint may carry that the model does not use.
     ignorable: Tuple[str, ...] = ()
 

@@ -31,6 +31,8 @@ def random_tensor(name: str, request: TensorRequest, seed: int, std: float,
     values = torch.randn(request.shape, generator=generator, dtype=torch.float32, device=device) * std
     if request.init == "around_one":
         values += 1.0
+    elif request.init == "positive":           # numbers of order one above zero (slopes, rates)
+        values = values.abs() / std * 0.5 + 0.05
     elif request.init != "normal":
         raise ValueError(f"unknown init '{request.init}' for tensor {name}")
     return values.to(dtype)

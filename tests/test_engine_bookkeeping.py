@@ -181,7 +181,10 @@ def test_flag_words_are_decoded_and_cleared(tmp_path):
             engine.check_flags()
         assert int(LoadedLibrary.error_flag) == 0 and int(engine.model.flags) == 0
         engine.model.flags[0] = 8
-        with pytest.raises(StepError, match=r"unknown bits 0x8"):
+        with pytest.raises(StepError, match=r"0x8 \(a position beyond the table of learned positions"):
+            engine.check_flags()
+        engine.model.flags[0] = 16
+        with pytest.raises(StepError, match=r"unknown bits 0x10"):
             engine.check_flags()
     finally:
         del ops._LOADED[("forged", 0)]
