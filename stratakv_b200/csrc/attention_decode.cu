@@ -57,7 +57,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                         int table_width, const int* __restrict__ ctx_after, __nv_bfloat16* __restrict__ out,
                         float* __restrict__ partial_o, float* __restrict__ partial_ml, int num_heads,
-                        int num_kv_heads, int block_size, float scale, int window, int splits, int m_tiles) {
+                        int num_kv_heads, int block_size, float scale, int window, int splits, int m_tiles,
+                        const AttentionExtras extras) {
     extern __shared__ float merge[];                  // [warps][16][DHD + 2]
     constexpr int PITCH = DHD + 2;
     pdl_launch_dependents();
@@ -137,7 +138,10 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int key = j0 + 8 * t + 2 * tig + (c & 1);
-                const float v = (key < ctx && key >= lo) ? s[t][c] * scale_log2 : -INFINITY;
+                float v = (key < ctx && key >= lo) ? s[t][c] * scale_log2 : -INFINITY;
+                if (extras.bias && key < ctx && key >= lo && g + 8 * (c >> 1) < rows)
+                    v = fmaf(-1.4426950408889634f,
+                             __ldg(extras.bias + (size_t)(head0 + g + 8 * (c >> 1)) * extras.bias_len + min(ctx - 1 - key, extras.bias_len - 1)), v);
                 s[t][c] = v;
                 tile_max[c >> 1] = fmaxf(tile_max[c >> 1], v);
             }
@@ -217,7 +221,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         }
         const int head = head0 + r;
         if (splits == 1) {
-            out[((size_t)seq * num_heads + head) * DHD + d] = __float2bfloat16_rn(total / sum);
+            out[((size_t)seq * num_heads + head) * DHD + d] = __float2bfloat16_rn(total / sum * gate_factor(extras, seq, head));
         } else {
             const size_t at = ((size_t)seq * num_heads + head) * splits + split;
             partial_o[at * DHD + d] = total;
@@ -228,10 +232,12 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 
 // out[seq, head, :] = sum_s e^(m_s - M) O_s / sum_s e^(m_s - M) l_s
 __global__ void decode_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
-                                      __nv_bfloat16* __restrict__ out, int splits) {
+                                      __nv_bfloat16* __restrict__ out, int splits, int num_heads,
+                                      const AttentionExtras extras) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t item = blockIdx.x;                   // seq * num_heads + head
+    const float gated = gate_factor(extras, item / num_heads, (int)(item % num_heads));
     float m = -INFINITY;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, partial_ml[2 * (item * splits + s)]);
     for (int d = threadIdx.x; d < DHD; d += blockDim.x) {
@@ -244,7 +250,7 @@ __global__ void decode_combine_kernel(const float* __restrict__ partial_o, const
             total += weight * partial_o[at * DHD + d];
             sum += weight * partial_ml[2 * at + 1];
         }
-        out[item * DHD + d] = __float2bfloat16_rn(total / sum);
+        out[item * DHD + d] = __float2bfloat16_rn(total / sum * gated);
     }
 }
 
@@ -254,12 +260,17 @@ using namespace skv;
 
 // Scratch the caller provides when splits > 1: partial_o [n_seqs * heads * splits * head_dim] floats,
 // partial_ml [n_seqs * heads * splits * 2] floats.
-SKV_EXPORT int skv_attention_decode(const void* q, const void* k_cache, const void* v_cache,
-                                    const int* block_table, int table_width, const int* ctx_after, void* out,
-                                    float* partial_o, float* partial_ml, int n_seqs, int num_heads,
-                                    int num_kv_heads, int head_dim, int block_size, float scale, int window,
-                                    int splits, cudaStream_t stream) {
+// `bias` [num_heads][bias_len] and `gate` (logits, rows gate_stride apart) may be null: see AttentionExtras.
+SKV_EXPORT int skv_attention_decode_extras(const void* q, const void* k_cache, const void* v_cache,
+                                           const int* block_table, int table_width, const int* ctx_after, void* out,
+                                           float* partial_o, float* partial_ml, int n_seqs, int num_heads,
+                                           int num_kv_heads, int head_dim, int block_size, float scale, int window,
+                                           int splits, const float* bias, int bias_len, const float* gate,
+                                           int gate_stride, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
+    if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads))
+        return fail("skv_attention_decode", "a bias table needs its length and a gate rows of at least heads numbers");
+    const AttentionExtras extras = {bias, bias_len, gate, gate_stride};
     if (head_dim != DHD) return fail("skv_attention_decode", "this library was built for another head size");
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_decode", "heads must be a positive multiple of kv heads");
@@ -285,13 +296,23 @@ SKV_EXPORT int skv_attention_decode(const void* q, const void* k_cache, const vo
                               stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
                               (const __nv_bfloat16*)v_cache, block_table, table_width, ctx_after,
                               (__nv_bfloat16*)out, partial_o, partial_ml, num_heads, num_kv_heads, block_size,
-                              scale, window, splits, m_tiles))
+                              scale, window, splits, m_tiles, extras))
         return code;
     if (splits > 1)
         return launch_pdl("skv_attention_decode(combine)", decode_combine_kernel, dim3(n_seqs * num_heads),
                           dim3(DHD >= 128 ? 128 : 64), 0, stream, (const float*)partial_o,
-                          (const float*)partial_ml, (__nv_bfloat16*)out, splits);
+                          (const float*)partial_ml, (__nv_bfloat16*)out, splits, num_heads, extras);
     return 0;
+}
+
+SKV_EXPORT int skv_attention_decode(const void* q, const void* k_cache, const void* v_cache,
+                                    const int* block_table, int table_width, const int* ctx_after, void* out,
+                                    float* partial_o, float* partial_ml, int n_seqs, int num_heads,
+                                    int num_kv_heads, int head_dim, int block_size, float scale, int window,
+                                    int splits, cudaStream_t stream) {
+    return skv_attention_decode_extras(q, k_cache, v_cache, block_table, table_width, ctx_after, out, partial_o,
+                                       partial_ml, n_seqs, num_heads, num_kv_heads, head_dim, block_size, scale, window,
+                                       splits, nullptr, 0, nullptr, 0, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -374,12 +395,12 @@ SKV_EXPORT int skv_attention_decode_no_alloc(const void* q, const void* k_cache,
                               smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
                               (const __nv_bfloat16*)v_cache, block_table, table_width, ctx_after,
                               (__nv_bfloat16*)out, partial_o, partial_ml, num_heads, num_kv_heads, block_size,
-                              scale, window, splits, m_tiles))
+                              scale, window, splits, m_tiles, AttentionExtras{nullptr, 0, nullptr, 0}))
         return code;
     if (splits > 1)
         return launch_pdl("skv_attention_decode_no_alloc(combine)", decode_combine_kernel,
                           dim3(n_seqs * num_heads), dim3(DHD >= 128 ? 128 : 64), 0, stream,
-                          (const float*)partial_o, (const float*)partial_ml, (__nv_bfloat16*)out, splits);
+                          (const float*)partial_o, (const float*)partial_ml, (__nv_bfloat16*)out, splits, num_heads, AttentionExtras{nullptr, 0, nullptr, 0});
     return 0;
 }
 
@@ -388,6 +409,12 @@ SKV_EXPORT int skv_attention_decode_no_alloc(const void* q, const void* k_cache,
 SKV_EXPORT int skv_attention_decode(const void*, const void*, const void*, const int*, int, const int*, void*,
                                     float*, float*, int, int, int, int, int, float, int, int, cudaStream_t) {
     return skv::fail("skv_attention_decode", "the float32 build decodes with skv_attention");
+}
+
+SKV_EXPORT int skv_attention_decode_extras(const void*, const void*, const void*, const int*, int, const int*, void*,
+                                           float*, float*, int, int, int, int, int, float, int, int, const float*, int,
+                                           const float*, int, cudaStream_t) {
+    return skv::fail("skv_attention_decode", "the float32 build has no split decode kernel: use skv_attention");
 }
 
 SKV_EXPORT long long skv_attention_decode_no_alloc_capacity() { return 0; }

@@ -64,7 +64,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                          int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_after,
                          __nv_bfloat16* __restrict__ out, int num_heads, int num_kv_heads, int block_size,
-                         float scale, int window, int tiles_per_seq) {
+                         float scale, int window, int tiles_per_seq, const AttentionExtras extras) {
     extern __shared__ __align__(16) uint8_t pf_smem[];      // [2 buffers][K tile | V tile]
     constexpr int TILE_ELEMS = PF_BN * PF_PITCH;
     __nv_bfloat16* tiles = (__nv_bfloat16*)pf_smem;
@@ -103,6 +103,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     }
     const int pos_top = ctx_before + row0 + g, pos_bottom = pos_top + 8;   // absolute positions of the two rows
     const float scale_log2 = scale * 1.4426950408889634f;                  // scores in units of log2
+    const float* bias_row = extras.bias ? extras.bias + (size_t)head * extras.bias_len : nullptr;
 
     auto load_tile = [&](int kt, int buffer) {
         __nv_bfloat16* k_dst = tiles + (size_t)buffer * 2 * TILE_ELEMS;
@@ -167,7 +168,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                     const int key = kt * PF_BN + 8 * n + 2 * tig + (c & 1);
                     const int pos = (c >> 1) ? pos_bottom : pos_top;
                     const bool seen = key <= pos && (window == 0 || key > pos - window);
-                    const float v = seen ? s[n][c] * scale_log2 : -INFINITY;
+                    float v = seen ? s[n][c] * scale_log2 : -INFINITY;
+                    if (bias_row && seen) v = fmaf(-1.4426950408889634f, __ldg(bias_row + min(pos - key, extras.bias_len - 1)), v);
                     s[n][c] = v;
                     tile_max[c >> 1] = fmaxf(tile_max[c >> 1], v);
                 }
@@ -223,7 +225,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
     }
     const int r_top = row0 + g, r_bottom = row0 + g + 8;
-    const float inv_top = 1.0f / row_sum[0], inv_bottom = 1.0f / row_sum[1];
+    const float inv_top = gate_factor(extras, q_begin + min(r_top, q_len - 1), head) / row_sum[0];
+    const float inv_bottom = gate_factor(extras, q_begin + min(r_bottom, q_len - 1), head) / row_sum[1];
 #pragma unroll
     for (int j = 0; j < PF_DTILES; ++j) {
         const int d = 8 * j + 2 * tig;
@@ -242,12 +245,17 @@ using namespace skv;
 
 // Sequences' new tokens are packed: sequence s owns rows cu_q[s] .. cu_q[s+1]-1 of q and out, and
 // ctx_after[s] keys are cached for it after this step's keys were written.
-SKV_EXPORT int skv_attention_prefill(const void* q, const void* k_cache, const void* v_cache,
-                                     const int* block_table, int table_width, const int* cu_q,
-                                     const int* ctx_after, void* out, int n_seqs, int max_q_len, int num_heads,
-                                     int num_kv_heads, int head_dim, int block_size, float scale, int window,
-                                     cudaStream_t stream) {
+// `bias` [num_heads][bias_len] and `gate` (logits, rows gate_stride apart) may be null: see AttentionExtras.
+SKV_EXPORT int skv_attention_prefill_extras(const void* q, const void* k_cache, const void* v_cache,
+                                            const int* block_table, int table_width, const int* cu_q,
+                                            const int* ctx_after, void* out, int n_seqs, int max_q_len, int num_heads,
+                                            int num_kv_heads, int head_dim, int block_size, float scale, int window,
+                                            const float* bias, int bias_len, const float* gate, int gate_stride,
+                                            cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
+    if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads))
+        return fail("skv_attention_prefill", "a bias table needs its length and a gate rows of at least heads numbers");
+    const AttentionExtras extras = {bias, bias_len, gate, gate_stride};
     if (head_dim != PHD) return fail("skv_attention_prefill", "this library was built for another head size");
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_prefill", "heads must be a positive multiple of kv heads");
@@ -268,7 +276,17 @@ SKV_EXPORT int skv_attention_prefill(const void* q, const void* k_cache, const v
     return launch_pdl("skv_attention_prefill", prefill_attention_kernel, dim3((unsigned)blocks, num_heads),
                       dim3(PF_WARPS * 32), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
                       (const __nv_bfloat16*)v_cache, block_table, table_width, cu_q, ctx_after, (__nv_bfloat16*)out,
-                      num_heads, num_kv_heads, block_size, scale, window, tiles_per_seq);
+                      num_heads, num_kv_heads, block_size, scale, window, tiles_per_seq, extras);
+}
+
+SKV_EXPORT int skv_attention_prefill(const void* q, const void* k_cache, const void* v_cache,
+                                     const int* block_table, int table_width, const int* cu_q,
+                                     const int* ctx_after, void* out, int n_seqs, int max_q_len, int num_heads,
+                                     int num_kv_heads, int head_dim, int block_size, float scale, int window,
+                                     cudaStream_t stream) {
+    return skv_attention_prefill_extras(q, k_cache, v_cache, block_table, table_width, cu_q, ctx_after, out, n_seqs,
+                                        max_q_len, num_heads, num_kv_heads, head_dim, block_size, scale, window,
+                                        nullptr, 0, nullptr, 0, stream);
 }
 
 SKV_EXPORT int skv_has_attention_prefill() { return 1; }
@@ -277,6 +295,12 @@ SKV_EXPORT int skv_has_attention_prefill() { return 1; }
 
 SKV_EXPORT int skv_attention_prefill(const void*, const void*, const void*, const int*, int, const int*, const int*,
                                      void*, int, int, int, int, int, int, float, int, cudaStream_t) {
+    return skv::fail("skv_attention_prefill", "this build (float32, or a head size above 128) uses skv_attention");
+}
+
+SKV_EXPORT int skv_attention_prefill_extras(const void*, const void*, const void*, const int*, int, const int*,
+                                            const int*, void*, int, int, int, int, int, int, float, int, const float*,
+                                            int, const float*, int, cudaStream_t) {
     return skv::fail("skv_attention_prefill", "this build (float32, or a head size above 128) uses skv_attention");
 }
 

@@ -146,7 +146,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                             int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_after,
                             __nv_bfloat16* __restrict__ out, int num_heads, int num_kv_heads, int block_size,
-                            int rows_per_load, float scale, int window, int tiles_per_seq, int* __restrict__ flag) {
+                            int rows_per_load, float scale, int window, int tiles_per_seq, int* __restrict__ flag,
+                            const AttentionExtras extras) {
     extern __shared__ uint8_t a_raw[];
     uint8_t* base = (uint8_t*)(((uintptr_t)a_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_tile = base;                                        // ACH tiles of 128 rows
@@ -306,6 +307,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int pos = ctx_before + q_row;
         const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
         const float scale_log2 = scale * 1.4426950408889634f;
+        // with a bias by distance the scores are brought to units of log2 when the bias is taken off them,
+        // and what follows multiplies by one
+        const float* bias_row = extras.bias ? extras.bias + (size_t)head * extras.bias_len : nullptr;
+        const float unit = bias_row ? 1.0f : scale_log2;
         float used_max = -INFINITY, row_sum = 0.0f;                   // in units of log2, after the scale
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
@@ -336,13 +341,20 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     sc[32 + e] = visible(key0 + 32 + e) ? __uint_as_float(v1[e]) : -INFINITY;
                 }
             }
+            if (bias_row) {
+#pragma unroll
+                for (int e = 0; e < ABN; ++e) {                        // (a masked score stays -infinity)
+                    const int distance = min(max(pos - key0 - e, 0), extras.bias_len - 1);
+                    sc[e] = fmaf(sc[e], scale_log2, -1.4426950408889634f * __ldg(bias_row + distance));
+                }
+            }
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int e = 0; e < ABN; e += 8) {                         // (three-input maxima: two scores an instruction)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) m4[c] = a_max3(m4[c], sc[e + 2 * c], sc[e + 2 * c + 1]);
             }
-            const float tile_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale_log2;   // scale > 0
+            const float tile_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * unit;   // scale > 0
             // raise the maximum in use (and rescale what has been accumulated) only when it matters
             const bool raise = tile_max > used_max + RESCALE_MARGIN;
             if (j > 0 && __any_sync(0xffffffffu, raise)) {
@@ -376,7 +388,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     // (a masked score is -infinity, the offset is finite and the scale positive: 2^-infinity = 0)
-                    p[e] = a_exp2(fmaf(sc[8 * piece + e], scale_log2, -offset));
+                    p[e] = a_exp2(fmaf(sc[8 * piece + e], unit, -offset));
                     s4[e & 3] += p[e];
                 }
                 uint32_t packed[4];
@@ -397,7 +409,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok && n_tiles > 0) ok = a_wait(bar(B_PE, (n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, flag);
         if (ok && n_tiles > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inverse = 1.0f / row_sum;
+            const float inverse = gate_factor(extras, q_begin + min(q_row, q_len - 1), head) / row_sum;
             __nv_bfloat16* dst = out + ((size_t)(q_begin + min(q_row, q_len - 1)) * num_heads + head) * AHD;
 #pragma unroll 1
             for (int c = 0; c < AHD; c += 32) {
@@ -479,12 +491,17 @@ using namespace skv;
 
 // As skv_attention_prefill; cache_blocks is the number of blocks of the layer's cache tensors
 // [cache_blocks][kv_heads][block_size][head_dim]; n_tokens the rows of q and out.
-SKV_EXPORT int skv_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, int cache_blocks,
-                                        const int* block_table, int table_width, const int* cu_q,
-                                        const int* ctx_after, void* out, int n_seqs, int n_tokens, int max_q_len,
-                                        int num_heads, int num_kv_heads, int head_dim, int block_size, float scale,
-                                        int window, int* flag, cudaStream_t stream) {
+// `bias` [num_heads][bias_len] and `gate` (logits, rows gate_stride apart) may be null: see AttentionExtras.
+SKV_EXPORT int skv_attention_prefill_tc_extras(const void* q, const void* k_cache, const void* v_cache, int cache_blocks,
+                                               const int* block_table, int table_width, const int* cu_q,
+                                               const int* ctx_after, void* out, int n_seqs, int n_tokens, int max_q_len,
+                                               int num_heads, int num_kv_heads, int head_dim, int block_size, float scale,
+                                               int window, const float* bias, int bias_len, const float* gate,
+                                               int gate_stride, int* flag, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
+    if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads))
+        return fail("skv_attention_prefill_tc", "a bias table needs its length and a gate rows of at least heads numbers");
+    const AttentionExtras extras = {bias, bias_len, gate, gate_stride};
     if (head_dim != AHD) return fail("skv_attention_prefill_tc", "this library was built for another head size");
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_prefill_tc", "heads must be a positive multiple of kv heads");
@@ -512,7 +529,17 @@ SKV_EXPORT int skv_attention_prefill_tc(const void* q, const void* k_cache, cons
     return launch_pdl("skv_attention_prefill_tc", prefill_attention_tc_kernel, dim3(num_heads, (unsigned)blocks),
                       dim3(ATHREADS), smem, stream, map_q, map_k, map_v, block_table, table_width, cu_q, ctx_after,
                       (__nv_bfloat16*)out, num_heads, num_kv_heads, block_size, rows_per_load, scale, window,
-                      tiles_per_seq, flag);
+                      tiles_per_seq, flag, extras);
+}
+
+SKV_EXPORT int skv_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, int cache_blocks,
+                                        const int* block_table, int table_width, const int* cu_q,
+                                        const int* ctx_after, void* out, int n_seqs, int n_tokens, int max_q_len,
+                                        int num_heads, int num_kv_heads, int head_dim, int block_size, float scale,
+                                        int window, int* flag, cudaStream_t stream) {
+    return skv_attention_prefill_tc_extras(q, k_cache, v_cache, cache_blocks, block_table, table_width, cu_q, ctx_after,
+                                           out, n_seqs, n_tokens, max_q_len, num_heads, num_kv_heads, head_dim, block_size,
+                                           scale, window, nullptr, 0, nullptr, 0, flag, stream);
 }
 
 SKV_EXPORT int skv_has_attention_prefill_tc() { return 1; }
@@ -522,6 +549,12 @@ SKV_EXPORT int skv_has_attention_prefill_tc() { return 1; }
 SKV_EXPORT int skv_attention_prefill_tc(const void*, const void*, const void*, int, const int*, int, const int*,
                                         const int*, void*, int, int, int, int, int, int, int, float, int, int*,
                                         cudaStream_t) {
+    return skv::fail("skv_attention_prefill_tc", "this build (float32, or a head size other than 64 or 128) has no such kernel");
+}
+
+SKV_EXPORT int skv_attention_prefill_tc_extras(const void*, const void*, const void*, int, const int*, int, const int*,
+                                               const int*, void*, int, int, int, int, int, int, int, float, int,
+                                               const float*, int, const float*, int, int*, cudaStream_t) {
     return skv::fail("skv_attention_prefill_tc", "this build (float32, or a head size other than 64 or 128) has no such kernel");
 }
 

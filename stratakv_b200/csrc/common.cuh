@@ -134,6 +134,23 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
     return __float2bfloat16_rn(v);
 }
 
+// Two optional terms of an attention kernel, both off when their pointer is null.
+//   bias:  a table [num_heads][bias_len]; bias[h][d] is taken off the score of a key at distance d from the
+//          query (a distance beyond the table reads its last entry).  Natural units (the kernels that keep their
+//          scores in units of log2 multiply by log2 e).
+//   gate:  the logit of (token t, head h) at gate[t * gate_stride + h]; the head's output is multiplied by its sigmoid.
+struct AttentionExtras {
+    const float* bias;
+    int bias_len;
+    const float* gate;
+    int gate_stride;
+};
+
+__device__ __forceinline__ float gate_factor(const AttentionExtras& extras, size_t token, int head) {
+    if (!extras.gate) return 1.0f;
+    return 1.0f / (1.0f + expf(-extras.gate[token * extras.gate_stride + head]));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);

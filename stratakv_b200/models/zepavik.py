@@ -30,7 +30,7 @@ def zepavik_spec(config: ZepavikConfig) -> ModelSpec:
             window=layer.window, v_head_dim=layer.vdim,
             q_bias=p + "mix.q.b", k_bias=p + "mix.k.b", v_bias=p + "mix.v.b",
             value_norm_eps=config.norm_eps,
-            distance_bias=DistanceBiasSpec(p + "mix.r1", p + "mix.r2"),
+            distance_bias=DistanceBiasSpec(p + "mix.r1", p + "mix.r2", max_distance=config.max_positions),
             gate_weight=p + "mix.g")
         ffn = None
         if layer.ff:

@@ -276,14 +276,28 @@ class Kernels:
             _ptr(token_seq), _ptr(out), n, num_heads, num_kv_heads, head_dim, block_size,
             ctypes.c_float(scale), window, _stream()), "attention")
 
+    def _extras(self, bias, gate, gate_stride: int, num_heads: int, name: str):
+        """Arguments (bias table, its length, gate logits, their row stride) of the attention kernels' optional terms."""
+        bias_len = 0
+        if bias is not None:
+            self._want(bias, torch.float32, "bias")
+            if bias.dim() != 2 or bias.shape[0] != num_heads or bias.shape[1] < 1:
+                raise KernelError(f"{name}: the bias table must be [heads, distances]")
+            bias_len = bias.shape[1]
+        if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda or gate_stride < num_heads):
+            raise KernelError(f"{name}: the gate must be float32 on the GPU, a row at least heads wide")
+        return _ptr(bias), bias_len, _ptr(gate), int(gate_stride) if gate is not None else 0
+
     def has_attention_prefill(self) -> bool:
         return bool(self.lib.skv_has_attention_prefill())
 
     def attention_prefill(self, q, k_cache, v_cache, block_table, cu_q, ctx_after, out, max_q_len: int,
                           num_heads: int, num_kv_heads: int, head_dim: int, block_size: int, scale: float,
-                          window: int = 0):
+                          window: int = 0, bias=None, gate=None, gate_stride: int = 0):
         """Many new tokens per sequence (bfloat16 build, head size up to 128): sequence ``s`` owns rows
-        ``cu_q[s]..cu_q[s+1]-1`` of ``q``/``out``; ``ctx_after[s]`` keys are cached, this step's included."""
+        ``cu_q[s]..cu_q[s+1]-1`` of ``q``/``out``; ``ctx_after[s]`` keys are cached, this step's included.
+        ``bias`` (float32 ``[heads, distances]``): ``bias[h, i - j]`` is taken off the score of query i and key j.
+        ``gate`` (float32 logits, token t and head h at ``[t * gate_stride + h]``): the output times its sigmoid."""
         self._want(q, self.dtype, "q"); self._want(out, self.dtype, "out")
         self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
         self._want(block_table, torch.int32, "block_table"); self._want(cu_q, torch.int32, "cu_q")
@@ -291,17 +305,18 @@ class Kernels:
         n_seqs = ctx_after.numel()
         if cu_q.numel() != n_seqs + 1 or block_table.shape[0] != n_seqs:
             raise KernelError("attention_prefill: one length, one offset pair and one table row per sequence is needed")
-        self._check(self.lib.skv_attention_prefill(
+        self._check(self.lib.skv_attention_prefill_extras(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
             _ptr(ctx_after), _ptr(out), n_seqs, max_q_len, num_heads, num_kv_heads, head_dim, block_size,
-            ctypes.c_float(scale), window, _stream()), "attention_prefill")
+            ctypes.c_float(scale), window, *self._extras(bias, gate, gate_stride, num_heads, "attention_prefill"),
+            _stream()), "attention_prefill")
 
     def has_attention_prefill_tc(self) -> bool:
         return bool(self.lib.skv_has_attention_prefill_tc())
 
     def attention_prefill_tc(self, q, k_cache, v_cache, block_table, cu_q, ctx_after, out, max_q_len: int,
                              num_heads: int, num_kv_heads: int, head_dim: int, block_size: int, scale: float,
-                             window: int = 0, flag=None):
+                             window: int = 0, flag=None, bias=None, gate=None, gate_stride: int = 0):
         """``attention_prefill`` with both products on the tcgen05 tensor cores (bfloat16, head size 64 or 128)."""
         self._want(q, self.dtype, "q"); self._want(out, self.dtype, "out")
         self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
@@ -312,16 +327,18 @@ class Kernels:
             raise KernelError("attention_prefill_tc: one length, one offset pair and one table row per sequence is needed")
         if tuple(k_cache.shape[1:]) != (num_kv_heads, block_size, head_dim) or k_cache.shape != v_cache.shape:
             raise KernelError("attention_prefill_tc: the cache must be [blocks, kv_heads, block_size, head_dim]")
-        self._check(self.lib.skv_attention_prefill_tc(
+        self._check(self.lib.skv_attention_prefill_tc_extras(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table), block_table.shape[1],
             _ptr(cu_q), _ptr(ctx_after), _ptr(out), n_seqs, q.shape[0], max_q_len, num_heads, num_kv_heads, head_dim,
-            block_size, ctypes.c_float(scale), window, _ptr(flag if flag is not None else self.error_flag),
-            _stream()), "attention_prefill_tc")
+            block_size, ctypes.c_float(scale), window,
+            *self._extras(bias, gate, gate_stride, num_heads, "attention_prefill_tc"),
+            _ptr(flag if flag is not None else self.error_flag), _stream()), "attention_prefill_tc")
 
     def attention_decode(self, q, k_cache, v_cache, block_table, ctx_after, out, num_heads: int,
                          num_kv_heads: int, head_dim: int, block_size: int, scale: float, window: int = 0,
-                         splits: int = 1, scratch_o=None, scratch_ml=None):
-        """One new token per sequence (bfloat16 build): ``ctx_after[s]`` keys are cached for sequence
+                         splits: int = 1, scratch_o=None, scratch_ml=None, bias=None, gate=None, gate_stride: int = 0):
+        """(``bias``, ``gate``: as in ``attention_prefill``.)
+        One new token per sequence (bfloat16 build): ``ctx_after[s]`` keys are cached for sequence
         ``s``, the newest being the query's own.  ``splits`` > 1 cuts each context across blocks and
         needs float scratch: ``scratch_o`` [seqs*heads*splits*head_dim], ``scratch_ml`` [seqs*heads*splits*2]."""
         self._want(q, self.dtype, "q"); self._want(out, self.dtype, "out")
@@ -334,10 +351,11 @@ class Kernels:
             self._want(scratch_o, torch.float32, "scratch_o"); self._want(scratch_ml, torch.float32, "scratch_ml")
             if scratch_o.numel() < n * num_heads * splits * head_dim or scratch_ml.numel() < n * num_heads * splits * 2:
                 raise KernelError("attention_decode: scratch is too small for this many splits")
-        self._check(self.lib.skv_attention_decode(
+        self._check(self.lib.skv_attention_decode_extras(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(ctx_after),
             _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), n, num_heads, num_kv_heads, head_dim, block_size,
-            ctypes.c_float(scale), window, splits, _stream()), "attention_decode")
+            ctypes.c_float(scale), window, splits, *self._extras(bias, gate, gate_stride, num_heads, "attention_decode"),
+            _stream()), "attention_decode")
 
     def has_attention_decode_fused(self) -> bool:
         return bool(self.lib.skv_has_attention_decode_fused())

@@ -139,6 +139,24 @@ class PagedAttention(Mixer):
         self.q_bias, self.k_bias, self.v_bias = as_float(s.q_bias), as_float(s.k_bias), as_float(s.v_bias)
         self.r1 = as_float(s.distance_bias.r1) if s.distance_bias else None
         self.r2 = as_float(s.distance_bias.r2) if s.distance_bias else None
+        self.bias_table = None
+        if s.distance_bias and self._specialised():
+            # what the bias takes off a score, by head and distance, for the kernels that look it up: as far as the
+            # window reaches, or as far as the model's positions do
+            reach = min(s.window or s.distance_bias.max_distance, s.distance_bias.max_distance or s.window)
+            if reach > 0:
+                r1 = tensors[s.distance_bias.r1].to(torch.float64)[:, None]
+                r2 = tensors[s.distance_bias.r2].to(torch.float64)[:, None]
+                table = r1 * torch.log1p(r2 * torch.arange(reach, dtype=torch.float64)[None, :])
+                self.bias_table = self.rt.upload(table.to(torch.float32).contiguous(), torch.float32)
+
+    def _specialised(self) -> bool:
+        """True if the kernels that are compiled for one head size can serve this mixer: bfloat16, keys and values
+        of one width that a library can be built for, and a distance bias (if any) that fits a table."""
+        s = self.spec
+        return (self.rt.dtype == torch.bfloat16 and s.value_dim == s.head_dim and s.head_dim % 16 == 0
+                and s.head_dim <= 256 and self.rt.device.type == "cuda"
+                and (not s.distance_bias or s.window > 0 or s.distance_bias.max_distance > 0))
 
     def _forward_extended(self, step, h, x, cache_entry, writes_cache=True):
         """The mixer with any of the further mechanisms: one projection for queries, keys, values and the gates'
@@ -156,10 +174,45 @@ class PagedAttention(Mixer):
                        self.v_bias, s.value_norm_eps, writes_cache)
         ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
         gate = fused[:, self.gate_offset:] if s.gate_weight else None
+        if self._specialised() and self._attend_specialised(step, q, ctx, k_cache, v_cache, table, gate):
+            ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
+            return
         ops.attention_general(q, k_cache, v_cache, table, step.positions, step.token_seq, ctx, s.num_heads,
                               s.num_kv_heads, s.head_dim, s.value_dim, step.cache.block_size, s.scale, s.window,
                               self.r1, self.r2, gate, self.fused_width)
         ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
+
+    def _attend_specialised(self, step, q, ctx, k_cache, v_cache, table, gate) -> bool:
+        """Attention through the kernels of the head size's own library, which take the distance bias as a table and
+        the gate's logits: split decode, or prefill on the tensor cores.  False if none of them serves this step."""
+        s, rt = self.spec, self.rt
+        ops = rt.kernels(s.head_dim)
+        n = q.shape[0]
+        extras = dict(bias=self.bias_table, gate=gate, gate_stride=self.fused_width)
+        block_size = step.cache.block_size
+        if step.is_decode:
+            if block_size % 16 != 0:
+                return False
+            blocks_per_seq = s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16))
+            keys = min(step.max_ctx, s.window) if s.window > 0 else step.max_ctx
+            splits = decode_splits(n, blocks_per_seq, keys, rt.sm_count)
+            scratch_o = scratch_ml = None
+            if splits > 1:
+                scratch_o = rt.workspace.get("attn_split_o", (n * s.num_heads * splits * s.head_dim,), torch.float32)
+                scratch_ml = rt.workspace.get("attn_split_ml", (n * s.num_heads * splits * 2,), torch.float32)
+            ops.attention_decode(q, k_cache, v_cache, table, step.ctx_after, ctx, s.num_heads, s.num_kv_heads,
+                                 s.head_dim, block_size, s.scale, s.window, splits, scratch_o, scratch_ml, **extras)
+            return True
+        if (ops.has_attention_prefill_tc() and step.max_q_len > 32 and block_size & (block_size - 1) == 0
+                and block_size >= 16 and step.n_seqs * -(-step.max_q_len // 128) <= 65535):
+            ops.attention_prefill_tc(q, k_cache, v_cache, table, step.cu_q, step.ctx_after, ctx, step.max_q_len,
+                                     s.num_heads, s.num_kv_heads, s.head_dim, block_size, s.scale, s.window, **extras)
+            return True
+        if ops.has_attention_prefill() and s.num_heads <= 65535:
+            ops.attention_prefill(q, k_cache, v_cache, table, step.cu_q, step.ctx_after, ctx, step.max_q_len,
+                                  s.num_heads, s.num_kv_heads, s.head_dim, block_size, s.scale, s.window, **extras)
+            return True
+        return False
 
     def forward(self, step, h, x, cache_entry, writes_cache=True):
         if self.spec.extended:

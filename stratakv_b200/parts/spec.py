@@ -36,6 +36,7 @@ class DistanceBiasSpec:
     ``(q.k) * scale - r1[h] * ln(1 + r2[h] * (i - j))`` with two learned numbers per head."""
     r1: str                          # tensor names, each [num_heads]
     r2: str
+    max_distance: int = 0            # the longest distance a model can reach (its positions); 0: unknown
     kind: str = "log_distance"
 
 

@@ -58,7 +58,7 @@ def random_tokens(vocab, length, seed):
     return torch.randint(0, vocab, (length,), generator=generator).tolist()
 
 
-def run_trace(model_dir, dtype, steps, out_dir, max_tokens, timeout=600, random_seed=None):
+def run_trace(model_dir, dtype, steps, out_dir, max_tokens, timeout=600, random_seed=None, vocab=None):
     """Run bin/trace_run on ``steps`` (a list of dicts); returns {step: array [wanted, vocab]}.
     ``random_seed``: no checkpoint is read; ``--random <model_dir>/config.json --seed`` draws the weights."""
     out_dir = Path(out_dir)
@@ -72,7 +72,7 @@ def run_trace(model_dir, dtype, steps, out_dir, max_tokens, timeout=600, random_
     assert result.returncode == 0, result.stderr[-4000:]
     done = [line for line in result.stdout.splitlines() if line.startswith("done ")]
     assert [line.split()[1] for line in done] == [str(s["step"]) for s in steps], result.stdout
-    vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
+    vocab = vocab or json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
     logits = {}
     for s in steps:
         wanted = sum(len(e.get("want", [])) for e in s["entries"])

@@ -10,6 +10,9 @@ from __future__ import annotations
 import torch
 
 MODE_STORE, MODE_STORE_F32, MODE_ADD_F32, MODE_GATED = 0, 1, 2, 3
+MODE_ACT = 5
+ACTIVATIONS = {"silu": lambda z: z * torch.sigmoid(z), "relu2": lambda z: torch.relu(z) ** 2,
+               "gelu_tanh": lambda z: torch.nn.functional.gelu(z, approximate="tanh")}
 
 
 class DoubleKernels:
@@ -37,6 +40,8 @@ class DoubleKernels:
             out.copy_((gate * torch.sigmoid(gate) * up).reshape(result.shape[0], -1).to(out.dtype))
         elif mode == MODE_ADD_F32:
             out.add_(result)
+        elif mode == MODE_ACT:
+            out.copy_(ACTIVATIONS[activation](result).to(out.dtype))
         else:
             out.copy_(result.to(out.dtype))
 
@@ -85,6 +90,72 @@ class DoubleKernels:
                 weights = torch.softmax((keys[:, g, :] @ qh[t, h]) * scale, dim=0)
                 result[t, h] = weights @ values[:, g, :]
         out.copy_(result.reshape(n, num_heads * head_dim).to(out.dtype))
+
+    def embed_sum(self, table, ids, out, positions, token_seq, cu_q, slot_ids, flag=None, pair_table=None,
+                  last_ids=None, mul_prev=0, mul_cur=0, position_table=None, position_scale=1.0):
+        self.calls.append("embed_sum")
+        x = table[ids.long()].float()
+        if pair_table is not None:
+            buckets = pair_table.shape[0] - 1
+            for t in range(ids.numel()):
+                seq, pos, row = int(token_seq[t]), int(positions[t]), buckets
+                if pos > 0:
+                    slot = int(slot_ids[seq])
+                    previous = int(ids[t - 1]) if t > int(cu_q[seq]) else int(last_ids[2 * slot + ((pos - 1) & 1)])
+                    row = (previous * mul_prev + int(ids[t]) * mul_cur) % buckets
+                x[t] += pair_table[row].float()
+            for seq in range(slot_ids.numel()):
+                last = int(cu_q[seq + 1]) - 1
+                last_ids[2 * int(slot_ids[seq]) + (int(positions[last]) & 1)] = ids[last]
+        if position_table is not None:
+            x += position_table[positions.long()].float() * position_scale
+        out.copy_(x)
+
+    def qkv_finish(self, qkv, q_out, k_cache, v_cache, positions, token_seq, block_table, num_heads, num_kv_heads,
+                   dim, vdim, block_size, q_bias=None, k_bias=None, v_bias=None, value_norm_eps=None, write_kv=True):
+        self.calls.append("qkv_finish")
+        n = qkv.shape[0]
+        a, b = num_heads * dim, (num_heads + num_kv_heads) * dim
+        q, k, v = qkv[:, :a], qkv[:, a:b], qkv[:, b:b + num_kv_heads * vdim]
+        q = q + q_bias if q_bias is not None else q
+        k = k + k_bias if k_bias is not None else k
+        v = (v + v_bias if v_bias is not None else v).view(n, num_kv_heads, vdim)
+        if value_norm_eps is not None:
+            v = v / torch.sqrt((v * v).mean(dim=-1, keepdim=True) + value_norm_eps)
+        q_out.copy_(q.to(q_out.dtype))
+        if write_kv:
+            k = k.view(n, num_kv_heads, dim)
+            for t in range(n):
+                pos = int(positions[t])
+                block = int(block_table[int(token_seq[t]), pos // block_size])
+                k_cache[block, :, pos % block_size, :] = k[t].to(k_cache.dtype)
+                v_cache[block, :, pos % block_size, :] = v[t].to(v_cache.dtype)
+
+    def attention_general(self, q, k_cache, v_cache, block_table, positions, token_seq, out, num_heads, num_kv_heads,
+                          dim, vdim, block_size, scale, window=0, r1=None, r2=None, gate=None, gate_stride=0):
+        self.calls.append("attention_general")
+        n = q.shape[0]
+        group = num_heads // num_kv_heads
+        qh = q.view(n, num_heads, dim).float()
+        out.zero_()
+        for t in range(n):
+            pos, seq = int(positions[t]), int(token_seq[t])
+            lo = max(0, pos - window + 1) if window > 0 else 0
+            where = [(int(block_table[seq, j // block_size]), j % block_size) for j in range(lo, pos + 1)]
+            keys = torch.stack([k_cache[b, :, r, :] for b, r in where]).float()
+            values = torch.stack([v_cache[b, :, r, :] for b, r in where]).float()
+            distance = torch.arange(pos - lo, -1, -1, dtype=torch.float32)
+            for h in range(num_heads):
+                score = (keys[:, h // group, :] @ qh[t, h]) * scale
+                if r1 is not None:
+                    score = score - r1[h] * torch.log1p(r2[h] * distance)
+                result = torch.softmax(score, dim=0) @ values[:, h // group, :]
+                if gate is not None:
+                    result = result * torch.sigmoid(gate[t, h])
+                out[t, h * vdim:(h + 1) * vdim] = result.to(out.dtype)
+
+    def scale_inplace(self, x, factor):
+        x.mul_(factor)
 
     def add_inplace(self, out, other):
         out.add_(other)

@@ -1,0 +1,209 @@
+"""The Zepavik decoder in the engine against the plain implementation (tests/plain_zepavik.py): whole prompts,
+prompts then tokens one by one, prompts in portions down to two tokens, batches of unequal requests with early
+finishers and slots used again, long decoding past windows and pages, greedy generation through Engine.generate,
+and the trace runner; in float32 and in bfloat16, on configurations that differ in every size."""
+import numpy as np
+import pytest
+import torch
+
+import plain_zepavik
+from helpers import random_tokens, run_trace, stored_dtype, tolerance
+from zepavik_models import ZEPAVIK, make_folder
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+NOISE = 0.04       # bfloat16: fraction of the logits' spread (measured at most 0.02; a lost key moves them by 0.2 and more)
+
+
+class Folders:
+    def __init__(self, root):
+        self.root, self.made, self.logits = root, {}, {}
+
+    def __getitem__(self, key):
+        name, dtype = key
+        if key not in self.made:
+            self.made[key] = make_folder(self.root / f"{name}_{dtype}", ZEPAVIK[name], seed=5 + list(ZEPAVIK).index(name),
+                                         dtype=stored_dtype(dtype))
+        return self.made[key]
+
+    def plain(self, name, dtype, tokens):
+        key = (name, dtype, tuple(tokens))
+        if key not in self.logits:
+            config, weights = plain_zepavik.load_folder(self[name, dtype])
+            self.logits[key] = plain_zepavik.logits_of(config, weights, list(tokens)).numpy()
+        return self.logits[key]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return Folders(tmp_path_factory.mktemp("zepavik"))
+
+
+def engine_for(folder, dtype, max_tokens=2048, block_size=64, **more):
+    from stratakv_b200 import Engine, EngineConfig
+    return Engine.from_folder(folder, EngineConfig(max_tokens=max_tokens, dtype=dtype, block_size=block_size, **more),
+                              verbose=False)
+
+
+def check(got, ref, dtype, what=""):
+    rtol, atol = tolerance(dtype, ref, noise=NOISE)
+    got = got.detach().float().cpu().numpy() if isinstance(got, torch.Tensor) else got
+    np.testing.assert_allclose(got, ref, rtol=rtol, atol=atol, err_msg=what)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(ZEPAVIK))
+def test_whole_prompts(folders, dtype, name):
+    from stratakv_b200 import StepEntry
+    engine = engine_for(folders[name, dtype], dtype)
+    for length in (1, 2, 3, 33, 64, 65, 150, 300):
+        tokens = random_tokens(ZEPAVIK[name]["vocab"], length, seed=length)
+        slot = engine.open_sequence()
+        got = engine.step([StepEntry(slot, tokens, list(range(length)))])
+        check(got, folders.plain(name, dtype, tokens), dtype, f"{name} whole length {length}")
+        engine.close_sequence(slot)
+    engine.check_flags()
+    assert engine.cache.all_free()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(ZEPAVIK))
+def test_prompt_then_tokens_one_by_one(folders, dtype, name):
+    """The first tokens of a sequence decoded alone (lengths 1 and 2), and decoding that starts inside a page,
+    runs over page borders and moves every window of the configuration past its first keys."""
+    from stratakv_b200 import StepEntry
+    engine = engine_for(folders[name, dtype], dtype)
+    for prompt, total in ((1, 40), (2, 10), (50, 140), (120, 330)):
+        tokens = random_tokens(ZEPAVIK[name]["vocab"], total, seed=total)
+        ref = folders.plain(name, dtype, tokens)
+        slot = engine.open_sequence()
+        got = engine.step([StepEntry(slot, tokens[:prompt], list(range(prompt)))])
+        check(got, ref[:prompt], dtype, f"{name} prompt of {prompt}")
+        for p in range(prompt, total):
+            got = engine.step([StepEntry(slot, [tokens[p]], [0])])
+            check(got, ref[p:p + 1], dtype, f"{name} position {p} decoded after a prompt of {prompt}")
+        engine.close_sequence(slot)
+    engine.check_flags()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(ZEPAVIK))
+def test_prompts_in_portions(folders, dtype, name):
+    from stratakv_b200 import StepEntry
+    engine = engine_for(folders[name, dtype], dtype)
+    for portions in ((70, 65, 40), (2, 2, 2, 2, 2), (63, 2, 1, 64, 33), (130, 2, 100)):
+        tokens = random_tokens(ZEPAVIK[name]["vocab"], sum(portions), seed=sum(portions))
+        ref = folders.plain(name, dtype, tokens)
+        slot, at = engine.open_sequence(), 0
+        for count in portions:
+            got = engine.step([StepEntry(slot, tokens[at:at + count], list(range(count)))])
+            check(got, ref[at:at + count], dtype, f"{name} portion {at}..{at + count} of {portions}")
+            at += count
+        engine.close_sequence(slot)
+    engine.check_flags()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(ZEPAVIK))
+def test_unequal_batches_with_early_finishers_and_reuse(folders, dtype, name):
+    """Two batches one after the other in one engine whose cache just holds one of them: the second takes the
+    slots and pages (and the embedding's per-sequence state) that the first gave back."""
+    from stratakv_b200 import StepEntry
+    vocab = ZEPAVIK[name]["vocab"]
+    engine = engine_for(folders[name, dtype], dtype, max_tokens=64 * 12, max_batch=4)
+    for batch, shapes in enumerate((((1, 5), (70, 12), (200, 30), (129, 31)), ((3, 33), (190, 3), (64, 40), (2, 1)))):
+        requests = [random_tokens(vocab, prompt + more, seed=100 * batch + i) for i, (prompt, more) in enumerate(shapes)]
+        refs = [folders.plain(name, dtype, tokens) for tokens in requests]
+        slots = [engine.open_sequence() for _ in requests]
+        got = engine.step([StepEntry(slot, tokens[:prompt], [prompt - 1])
+                           for slot, tokens, (prompt, _) in zip(slots, requests, shapes)])
+        for row, (ref, (prompt, _)) in enumerate(zip(refs, shapes)):
+            check(got[row:row + 1], ref[prompt - 1:prompt], dtype, f"{name} batch {batch} prompt {row}")
+        for step in range(max(more for _, more in shapes)):
+            live = [i for i, (_, more) in enumerate(shapes) if step < more]
+            got = engine.step([StepEntry(slots[i], [requests[i][shapes[i][0] + step]], [0]) for i in live])
+            for row, i in enumerate(live):
+                at = shapes[i][0] + step
+                check(got[row:row + 1], refs[i][at:at + 1], dtype, f"{name} batch {batch} request {i} position {at}")
+            for i in live:
+                if step + 1 == shapes[i][1]:
+                    engine.close_sequence(slots[i])
+        engine.check_flags()
+    assert engine.cache.all_free()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_pages_of_sixteen_and_windows_that_give_pages_back(folders, dtype):
+    """Small pages: every window of the configuration spans several, and pages behind a window go back to the
+    allocator while the sequence decodes (the cache holds fewer pages than the sequence has positions)."""
+    from stratakv_b200 import StepEntry
+    name = "ZA"
+    engine = engine_for(folders[name, dtype], dtype, max_tokens=16 * 6, block_size=16, max_batch=1, max_context=400)
+    tokens = random_tokens(ZEPAVIK[name]["vocab"], 260, seed=77)
+    ref = folders.plain(name, dtype, tokens)
+    slot = engine.open_sequence()
+    got = engine.step([StepEntry(slot, tokens[:30], [29])])
+    check(got, ref[29:30], dtype, "prompt")
+    for p in range(30, 260):
+        got = engine.step([StepEntry(slot, [tokens[p]], [0])])
+        check(got, ref[p:p + 1], dtype, f"position {p}")
+    engine.close_sequence(slot)
+    assert engine.cache.all_free()
+
+
+@pytest.mark.parametrize("name", ["ZA", "ZC"])
+def test_greedy_generation_through_the_engine(folders, name):
+    """Engine.generate (the scheduler, the graph steps that run ahead of the host, the sampler): every token it
+    chooses is the plain implementation's best or within rounding of it."""
+    dtype = "float32"
+    engine = engine_for(folders[name, dtype], dtype, max_tokens=1024)
+    vocab = ZEPAVIK[name]["vocab"]
+    prompts = [random_tokens(vocab, n, seed=900 + n) for n in (1, 9, 70)]
+    output = engine.generate(prompts, 24, ignore_eos=True)
+    config, weights = plain_zepavik.load_folder(folders[name, dtype])
+    for prompt, sequence in zip(prompts, output.sequences):
+        assert len(sequence) == len(prompt) + 24 and sequence[:len(prompt)] == prompt
+        logits = plain_zepavik.logits_of(config, weights, sequence).numpy()
+        for at in range(len(prompt), len(sequence)):
+            row = logits[at - 1]
+            assert row[sequence[at]] >= row.max() - 1e-4 * max(1.0, abs(row.max())), f"{name}: token {at} is not the best"
+    assert engine.cache.all_free()
+
+
+def test_generation_in_bfloat16_repeats_itself(folders):
+    """Generation through graphs and through eager steps chooses the same tokens (sequence state included)."""
+    name, dtype = "ZA", "bfloat16"
+    prompts = [random_tokens(ZEPAVIK[name]["vocab"], n, seed=40 + n) for n in (5, 31)]
+    outputs = []
+    for graphs in (True, False):
+        engine = engine_for(folders[name, dtype], dtype, max_tokens=512, use_cuda_graphs=graphs)
+        outputs.append(engine.generate(prompts, 20, ignore_eos=True).sequences)
+    assert outputs[0] == outputs[1]
+
+
+def test_positions_end_with_their_table(folders):
+    from stratakv_b200 import StepEntry
+    from stratakv_b200.engine.engine import StepError
+    engine = engine_for(folders["ZA", "float32"], "float32", max_tokens=1024, max_context=1024)
+    slot = engine.open_sequence()
+    limit = ZEPAVIK["ZA"]["max_positions"]
+    with pytest.raises(StepError, match="limit"):
+        engine.step([StepEntry(slot, random_tokens(96, limit + 1, seed=1), [])])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_runner_chooses_the_model_by_its_config(folders, dtype, tmp_path):
+    name = "ZB"
+    folder = folders[name, dtype]
+    a, b = random_tokens(131, 75, seed=1), random_tokens(131, 20, seed=2)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:70], "want": [0, 69]}, {"id": "b", "tokens": b[:18], "want": [17]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[70:71], "want": [0]}, {"id": "b", "tokens": b[18:19], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[71:72], "want": [0]}, {"id": "b", "tokens": b[19:20], "want": [0]}], "end": ["b"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[72:75], "want": [2]}], "end": ["a"]}]
+    logits = run_trace(folder, dtype, steps, tmp_path / "out", max_tokens=256, vocab=ZEPAVIK[name]["vocab"])
+    ref_a, ref_b = folders.plain(name, dtype, a), folders.plain(name, dtype, b)
+    check(logits[0], np.stack([ref_a[0], ref_a[69], ref_b[17]]), dtype, "step 0")
+    check(logits[1], ref_a[70:71], dtype, "step 1")
+    check(logits[2], np.stack([ref_a[71], ref_b[19]]), dtype, "step 2")
+    check(logits[3], ref_a[74:75], dtype, "step 3")
