@@ -1,6 +1,7 @@
 """Benchmark: decode tokens a second and prefill tokens a second on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+    python bench.py --design zepavik [--layers 8]       (the Zepavik decoder beside Llama at equal layer sizes)
 
 The default run has the layer sizes of the TinyLlama-1.1B shape (22 layers,
 hidden 2048, 32 heads, 4 KV heads, head size 64, feed-forward 5632, vocabulary
@@ -133,6 +134,86 @@ def make_engine(layers: int, max_tokens: int, max_batch: int, shape=None):
     engine = Engine(spec, tensors, engine_config, verbose=False)
     engine.model_config = config
     return engine, config
+
+
+def engine_of(config, max_tokens: int, max_batch: int):
+    """An engine with random bfloat16 weights (made on the device) for a typed configuration of any architecture."""
+    import torch
+    from stratakv_b200 import Engine, EngineConfig
+    from stratakv_b200.config.registry import resolve_architecture
+    from stratakv_b200.engine.model import expected_tensors
+    from stratakv_b200.weights import random_tensors
+    spec = resolve_architecture(config.architecture).build_spec(config)
+    tensors = random_tensors(expected_tensors(spec), seed=0, dtype=torch.bfloat16, device="cuda")
+    engine = Engine(spec, tensors, EngineConfig(max_tokens=max_tokens, dtype="bfloat16", max_batch=max_batch,
+                                                max_context=max_tokens), verbose=False)
+    engine.model_config = config
+    return engine
+
+
+# Layer sizes at which the Zepavik decoder is measured beside the Llama decoder: the same width, heads, KV heads,
+# head size, vocabulary and number of layers; the feed-forwards hold the same number of weights (Llama's has three
+# matrices, Zepavik's two, so its inner width is 3/2 of Llama's); Zepavik's window spans the whole context, so
+# both attend over the same keys.
+DESIGN_SIZES = {
+    "2048x32h4kv-d64": dict(hidden=2048, heads=32, kv_heads=4, head_dim=64, llama_ff=5632),
+    "4096x32h8kv-d128": dict(hidden=4096, heads=32, kv_heads=8, head_dim=128, llama_ff=14336),
+    "3072x24h24kv-d128": dict(hidden=3072, heads=24, kv_heads=24, head_dim=128, llama_ff=8192),
+}
+
+
+def design_arm(args) -> int:
+    """Prefill and decode of the Zepavik decoder and of the Llama decoder at equal layer sizes (random weights)."""
+    import gc
+    import torch
+    from stratakv_b200.config import LlamaConfig, ZepavikConfig
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device")
+        return 1
+    layers, vocab, context, batch = args.layers or 8, 32000, args.context, args.batch
+    steps, warmup = max(args.steps, 1), max(args.warmup, 3)
+    peak = peaks()
+    sizes = {}
+    sampler = ClockSampler()
+    sampler.start()
+    for name, size in DESIGN_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        llama = LlamaConfig.from_dict(dict(TINYLLAMA, hidden_size=size["hidden"], intermediate_size=size["llama_ff"],
+                                           num_hidden_layers=layers, num_attention_heads=size["heads"],
+                                           num_key_value_heads=size["kv_heads"], head_dim=size["head_dim"],
+                                           vocab_size=vocab, max_position_embeddings=context + 64))
+        mixer = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["head_dim"], "vdim": size["head_dim"],
+                 "scale": size["head_dim"] ** -0.5, "mask": {"size": args.window or context + 64}}
+        zepavik = ZepavikConfig.from_dict({
+            "architecture": "Zepavik", "vocab": vocab, "width": size["hidden"], "max_positions": context + 64,
+            "logit_scale": 1.0, "norm": {"eps": 1e-5},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 40503, "mul_cur": 9973}},
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": size["llama_ff"] * 3 // 2}}] * layers})
+        row = {}
+        for label, config in (("zepavik", zepavik), ("llama", llama)):
+            engine = engine_of(config, max(batch * (context + 64), PREFILL_TOKENS + 64), batch)
+            prefill_ms = time_prefill(engine, PREFILL_TOKENS, vocab)
+            decode_ms, launches, _ = time_decode(engine, batch, context - steps - warmup, steps, warmup, vocab)
+            weight_bytes = engine.model.weight_bytes()
+            kv_bytes = batch * min(context, args.window or context) * engine.cache.bytes_per_token()
+            row[label] = {"prefill_tokens_per_s": PREFILL_TOKENS * 1000.0 / prefill_ms, "prefill_ms": prefill_ms,
+                          "decode_tokens_per_s": batch * 1000.0 / decode_ms, "decode_ms_per_step": decode_ms,
+                          "decode_hbm_frac": (weight_bytes + kv_bytes) / (decode_ms * 1e-3) / 1e9 / peak["hbm_gbs"],
+                          "weight_bytes": weight_bytes, "launches_in_timed_steps": launches}
+            del engine
+            gc.collect()
+            torch.cuda.empty_cache()
+        row["prefill_ratio"] = row["zepavik"]["prefill_tokens_per_s"] / row["llama"]["prefill_tokens_per_s"]
+        row["decode_ratio"] = row["zepavik"]["decode_tokens_per_s"] / row["llama"]["decode_tokens_per_s"]
+        sizes[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"design": "Zepavik", "beside": "LlamaForCausalLM", "layers": layers, "vocab": vocab,
+                      "prefill_tokens": PREFILL_TOKENS, "decode_batch": batch, "context": context,
+                      "window": args.window or context + 64, "dtype": "bf16", "steps": steps, "warmup": warmup,
+                      "data": "synthetic: random N(0,0.02) weights, uniform random token ids", "peaks": peak,
+                      "clocks": clocks, "sizes": sizes}))
+    return 0
 
 
 def random_ids(count, vocab, seed):
@@ -432,6 +513,10 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
     parser.add_argument("--context", type=int, default=CONTEXT, help="context at which the timed decode steps end")
+    parser.add_argument("--design", choices=["zepavik"],
+                        help="measure this design beside the Llama decoder at equal layer sizes instead of the step benchmark")
+    parser.add_argument("--sizes", default="", help="with --design: names of DESIGN_SIZES, with commas (default: all)")
+    parser.add_argument("--window", type=int, default=0, help="with --design: the design's window (default: the whole context)")
     parser.add_argument("--workload", choices=sorted(WORKLOADS),
                         help="a whole generation workload through Engine.generate instead of the step benchmark")
     args = parser.parse_args()
@@ -440,6 +525,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.design:
+        return design_arm(args)
     if args.workload:
         return workload_arm(args)
     warmup = max(args.warmup, 3)

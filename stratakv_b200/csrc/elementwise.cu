@@ -66,7 +66,10 @@ __global__ void embed_sum_kernel(const T* __restrict__ table, const T* __restric
                                  const int* __restrict__ cu_q, const int* __restrict__ slot_ids,
                                  const int* __restrict__ last_ids, float* __restrict__ out, int hidden, int vocab,
                                  int buckets, long long mul_prev, long long mul_cur, int max_positions,
-                                 float position_scale, int* __restrict__ flag) {
+                                 float position_scale, int* __restrict__ flag, float* __restrict__ row_scale,
+                                 const float* __restrict__ gamma_next, float eps_next, T* __restrict__ scaled,
+                                 float* __restrict__ partials, int stride) {
+    __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -88,11 +91,23 @@ __global__ void embed_sum_kernel(const T* __restrict__ table, const T* __restric
     }
     const T* position_row = position_table && !beyond ? position_table + (size_t)pos * hidden : nullptr;
     float* row_out = out + (size_t)t * hidden;
+    float partial = 0.0f;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float v = bad ? 0.0f : to_float(row[c]);
         if (pair_row && !bad) v += to_float(pair_row[c]);
         if (position_row) v += to_float(position_row[c]) * position_scale;
         row_out[c] = v;
+        if (scaled) {                                 // what the projection after the first norm needs (as embed_kernel)
+            partial = fmaf(v, v, partial);
+            scaled[(size_t)t * hidden + c] = from_float<T>(v * gamma_next[c]);
+        }
+    }
+    if (scaled) {
+        const float total = block_sum(partial, scratch);
+        if (threadIdx.x == 0) {
+            partials[(size_t)t * stride] = total;
+            row_scale[t] = 1.0f / sqrtf(total / (float)hidden + eps_next);
+        }
     }
 }
 
@@ -399,21 +414,26 @@ SKV_EXPORT int skv_embed(const void* table, const int* ids, float* out, int n_to
 
 // `pair_table` [buckets + 1, hidden] and `position_table` [max_positions, hidden] may be null (that term is left out).
 // `last_ids` holds two ids per sequence slot; it is read here and brought up to date by a second launch.
+// `scaled` and what follows it: as in skv_embed (the folded first norm), or null.
 SKV_EXPORT int skv_embed_sum(const void* table, const void* pair_table, const void* position_table, const int* ids,
                              const int* positions, const int* token_seq, const int* cu_q, const int* slot_ids,
                              int* last_ids, float* out, int n_tokens, int n_seqs, int hidden, int vocab, int buckets,
                              long long mul_prev, long long mul_cur, int max_positions, float position_scale,
-                             int* flag, cudaStream_t stream) {
+                             int* flag, void* scaled, const float* gamma_next, float* partials, int partial_stride,
+                             float* row_scale, float eps_next, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hidden <= 0 || vocab <= 0 || n_seqs <= 0) return fail("skv_embed_sum", "hidden, vocab and the number of sequences must be positive");
     if (pair_table && (buckets <= 0 || !last_ids || !cu_q || !slot_ids || !token_seq))
         return fail("skv_embed_sum", "a pair table needs its number of buckets and the sequences' last ids");
     if (position_table && max_positions <= 0) return fail("skv_embed_sum", "a position table needs its length");
+    if (scaled && (!gamma_next || !partials || !row_scale || partial_stride < 1))
+        return fail("skv_embed_sum", "the next norm's weight and places for the sums of squares and the factors are needed");
     const int threads = hidden >= 1024 ? 256 : 128;
     if (int code = launch_pdl("skv_embed_sum", embed_sum_kernel<skv_t>, dim3(n_tokens), dim3(threads), 0, stream,
                               (const skv_t*)table, (const skv_t*)pair_table, (const skv_t*)position_table, ids,
                               positions, token_seq, cu_q, slot_ids, (const int*)last_ids, out, hidden, vocab, buckets,
-                              mul_prev, mul_cur, max_positions, position_scale, flag))
+                              mul_prev, mul_cur, max_positions, position_scale, flag, row_scale, gamma_next, eps_next,
+                              (skv_t*)scaled, partials, partial_stride))
         return code;
     if (!pair_table) return 0;
     return launch_pdl("skv_embed_sum", remember_last_ids_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, stream, ids,

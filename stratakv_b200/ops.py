@@ -383,11 +383,12 @@ class Kernels:
 
     def embed_sum(self, table, ids, out, positions, token_seq, cu_q, slot_ids, flag=None, pair_table=None,
                   last_ids=None, mul_prev: int = 0, mul_cur: int = 0, position_table=None,
-                  position_scale: float = 1.0):
+                  position_scale: float = 1.0, stats=None):
         """out[t, :] = table[ids[t]] + pair_table[bucket(previous id, ids[t])] + position_table[positions[t]] *
         position_scale, summed in float32; either of the two further tables may be None.  ``pair_table`` has one row
         per bucket and a last row for a sequence's first token; ``last_ids`` (int32, two per sequence slot: by the parity of the
-        position) holds the last ids each sequence brought to its steps before and is brought up to date."""
+        position) holds the last ids each sequence brought to its steps before and is brought up to date.
+        ``stats``: as in ``embed`` (the first norm folded into the projection after it)."""
         self._want(table, self.dtype, "table"); self._want(ids, torch.int32, "ids")
         self._want(out, torch.float32, "out"); self._want(positions, torch.int32, "positions")
         self._want(token_seq, torch.int32, "token_seq"); self._want(cu_q, torch.int32, "cu_q")
@@ -408,13 +409,16 @@ class Kernels:
             max_positions = position_table.shape[0]
             if position_table.shape[1] != hidden:
                 raise KernelError("embed_sum: the position table must be [positions, hidden]")
+        fold = self._fold_target(stats, n, hidden)
         self._check(self.lib.skv_embed_sum(
             _ptr(table), _ptr(pair_table), _ptr(position_table), _ptr(ids), _ptr(positions), _ptr(token_seq), _ptr(cu_q),
             _ptr(slot_ids), _ptr(last_ids), _ptr(out), n, n_seqs, hidden, table.shape[0], buckets,
             ctypes.c_longlong(mul_prev), ctypes.c_longlong(mul_cur), max_positions, ctypes.c_float(position_scale),
-            _ptr(flag), _stream()), "embed_sum")
+            _ptr(flag), *(fold[:6] if fold else _NO_FOLD[:6]), _stream()), "embed_sum")
         if pair_table is not None:
             Kernels.launches += 1              # (the second launch that remembers the last ids)
+        if stats is not None:
+            stats.filled(1 if stats.consumer_sums else 0) if fold else stats.invalidate()
 
     def qkv_finish(self, qkv, q_out, k_cache, v_cache, positions, token_seq, block_table, num_heads: int,
                    num_kv_heads: int, dim: int, vdim: int, block_size: int, q_bias=None, k_bias=None, v_bias=None,

@@ -58,10 +58,7 @@ def wants_more_pieces(n_seqs: int, blocks_per_seq: int, max_ctx: int, cluster_sp
 
 class PagedAttention(Mixer):
     graph_safe = True
-
-    @property
-    def folds_norm(self):
-        return not self.spec.extended
+    folds_norm = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -147,6 +144,7 @@ class PagedAttention(Mixer):
             if reach > 0:
                 r1 = tensors[s.distance_bias.r1].to(torch.float64)[:, None]
                 r2 = tensors[s.distance_bias.r2].to(torch.float64)[:, None]
+                r1, r2 = r1.cpu(), r2.cpu()         # (random weights may have been drawn on the device)
                 table = r1 * torch.log1p(r2 * torch.arange(reach, dtype=torch.float64)[None, :])
                 self.bias_table = self.rt.upload(table.to(torch.float32).contiguous(), torch.float32)
 

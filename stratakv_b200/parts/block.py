@@ -72,13 +72,19 @@ def parallel(layer: Layer, step, x, entry) -> None:
     if layer.mixer_norm is None or layer.mixer is None:
         raise ValueError("the parallel arrangement needs a norm and a mixer")
     stats = step.residual_stats
+    folding = stats is not None and layer.mixer.folds_norm and (layer.ffn is None or layer.ffn.folds_norm)
+    h = _normed(layer.mixer_norm, layer.mixer, step, x) if folding else layer.mixer_norm.forward(x)
+    # Both branches add to the stream; the one that adds last leaves what the next norm's consumer needs.  A
+    # norm handed over unfinished (``NormedRows``) stays readable for the second branch: the first one's
+    # residual sum is told to expect nobody and so leaves the rows it was computed from alone.
     if stats is not None:
-        stats.expect(None)                  # (both branches add to the stream: neither leaves the next norm's sums)
-    h = layer.mixer_norm.forward(x)
+        stats.expect(step.norm_after_layer if folding and layer.ffn is None else None)
     layer.mixer.forward(step, h, x, entry.cache, entry.writes_cache)
     if layer.ffn is not None:
+        if stats is not None:
+            stats.expect(step.norm_after_layer if folding else None)
         layer.ffn.forward(step, h, x)
-    if stats is not None:
+    if stats is not None and not folding:
         stats.invalidate()
 
 

@@ -75,9 +75,8 @@ class SummedEmbedding(Part):
             self.table, step.token_ids, x, step.positions, step.token_seq, step.cu_q, step.slot_ids, flags,
             pair_table=self.pair_table, last_ids=last_ids,
             mul_prev=s.pair.mul_prev if s.pair is not None else 0, mul_cur=s.pair.mul_cur if s.pair is not None else 0,
-            position_table=self.position_table, position_scale=s.positions.scale if s.positions is not None else 1.0)
-        if stats is not None:
-            stats.invalidate()
+            position_table=self.position_table, position_scale=s.positions.scale if s.positions is not None else 1.0,
+            stats=stats)
 
 
 class LinearHead(Part):

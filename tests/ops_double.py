@@ -92,7 +92,7 @@ class DoubleKernels:
         out.copy_(result.reshape(n, num_heads * head_dim).to(out.dtype))
 
     def embed_sum(self, table, ids, out, positions, token_seq, cu_q, slot_ids, flag=None, pair_table=None,
-                  last_ids=None, mul_prev=0, mul_cur=0, position_table=None, position_scale=1.0):
+                  last_ids=None, mul_prev=0, mul_cur=0, position_table=None, position_scale=1.0, stats=None):
         self.calls.append("embed_sum")
         x = table[ids.long()].float()
         if pair_table is not None:

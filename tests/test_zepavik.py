@@ -112,12 +112,14 @@ def test_the_plain_implementation_tells_faults_from_rounding(tmp_path):
     config, weights = plain_zepavik.load_folder(folder)
     tokens = random_tokens(ZEPAVIK[name]["vocab"], 90, seed=2)
     right = plain_zepavik.logits_of(config, weights, tokens).numpy()
-    allowed = 0.04 * right.std()
+    allowed = 0.06 * right.std()             # what tests/test_zepavik_gpu.py allows a position in bfloat16
 
     def moved(change):
+        """The most a position's logits move, root mean square over the vocabulary."""
         other_config, other_weights = copy.deepcopy(config), dict(weights)
         change(other_config, other_weights)
-        return np.abs(plain_zepavik.logits_of(other_config, other_weights, tokens).numpy() - right).max()
+        difference = plain_zepavik.logits_of(other_config, other_weights, tokens).numpy() - right
+        return np.sqrt((difference ** 2).mean(axis=-1)).max()
 
     def window_off_by_one(c, w): c["layers"][0]["mixer"]["mask"]["size"] += 1
     def no_distance_bias(c, w): w["l0.mix.r1"] = torch.zeros_like(w["l0.mix.r1"])
@@ -127,7 +129,7 @@ def test_the_plain_implementation_tells_faults_from_rounding(tmp_path):
     def other_pair_hash(c, w): c["embedding"]["bigram"]["mul_prev"] += 1
     def shifted_positions(c, w): w["pos"] = torch.roll(w["pos"], 1, dims=0)
     for change in (window_off_by_one, no_distance_bias, no_query_bias, no_value_bias, no_gate, other_pair_hash, shifted_positions):
-        assert moved(change) > 3 * allowed, change.__name__
+        assert moved(change) > 2 * allowed, change.__name__
     # (a bias on the keys adds the same number to all of a query's scores and cancels in the softmax)
     # the value norm: without it the values keep their own length
     v = torch.randn(5, 2, 16, dtype=torch.float64) * 3

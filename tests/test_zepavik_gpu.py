@@ -7,13 +7,18 @@ import pytest
 import torch
 
 import plain_zepavik
-from helpers import random_tokens, run_trace, stored_dtype, tolerance
+from helpers import random_tokens, run_trace, stored_dtype
 from zepavik_models import ZEPAVIK, make_folder
 
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-NOISE = 0.04       # bfloat16: fraction of the logits' spread (measured at most 0.02; a lost key moves them by 0.2 and more)
+# A position's logits may differ from the plain ones by this fraction of the logits' spread in the root mean square
+# over the vocabulary, and a single logit by four times that.  The test models' queries and keys are large, so that
+# attention is peaked: in bfloat16 their rounding moves a position by up to 0.046 of the spread (measured), while a
+# window that is one key off, a lost bias or another hash moves one by 0.13 to 0.4 (tests/test_zepavik.py shows that
+# on the plain implementation).  float32 differs by the order of its sums.
+ROW_NOISE = {"bfloat16": 0.06, "float32": 5e-5}
 
 
 class Folders:
@@ -47,9 +52,15 @@ def engine_for(folder, dtype, max_tokens=2048, block_size=64, **more):
 
 
 def check(got, ref, dtype, what=""):
-    rtol, atol = tolerance(dtype, ref, noise=NOISE)
     got = got.detach().float().cpu().numpy() if isinstance(got, torch.Tensor) else got
-    np.testing.assert_allclose(got, ref, rtol=rtol, atol=atol, err_msg=what)
+    assert got.shape == ref.shape, what
+    spread = float(np.asarray(ref, dtype=np.float64).std())
+    difference = got.astype(np.float64) - ref
+    per_position = np.sqrt((difference ** 2).mean(axis=-1))
+    worst = int(per_position.argmax())
+    allowed = ROW_NOISE[dtype] * spread
+    assert per_position[worst] <= allowed, f"{what}: row {worst} is off by {per_position[worst] / spread:.2e} of the spread"
+    assert np.abs(difference).max() <= 4 * allowed, f"{what}: a logit is off by {np.abs(difference).max() / spread:.2e} of the spread"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
