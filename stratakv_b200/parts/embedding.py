@@ -96,8 +96,9 @@ class LinearHead(Part):
         in scratch memory that the next step overwrites."""
         logits = self.rt.workspace.get("logits", (n_rows, self.spec.vocab_size), torch.float32)
         self.rt.kernels().linear(y, self.weight, logits, _ops.MODE_STORE_F32)
-        if self.spec.logit_scale != 1.0:
-            self.rt.kernels().scale_inplace(logits, self.spec.logit_scale)
+        scale = getattr(self.spec, "logit_scale", 1.0)         # (a head spec of another design may not have one)
+        if scale != 1.0:
+            self.rt.kernels().scale_inplace(logits, scale)
         return logits
 
 

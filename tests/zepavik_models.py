@@ -41,14 +41,18 @@ ZD = config(200, 96, [layer(8, 1, 32, 32, 0, 48), layer(2, 2, 32, 32, 33, 40)], 
 ZEPAVIK = {"ZA": ZA, "ZB": ZB, "ZC": ZC, "ZD": ZD}
 
 
-def make_folder(folder, raw_config, seed, dtype=torch.float32, sharpen=6.0):
-    """A model folder with random weights stored in ``dtype``; query and key matrices times ``sharpen``."""
+def make_folder(folder, raw_config, seed, dtype=torch.float32, sharpen=None):
+    """A model folder with random weights stored in ``dtype``; query and key matrices times ``sharpen``.
+    By default the factor is such that scores (before the design's scale, over sqrt(dim)) have a standard deviation of
+    about 6 at every width: peaked attention, with the same share of bfloat16 rounding in every configuration."""
     from stratakv_b200.config import ZepavikConfig
     from stratakv_b200.engine.model import expected_tensors
     from stratakv_b200.models.zepavik import zepavik_spec
     from stratakv_b200.weights.random_init import random_tensors
     from stratakv_b200.weights.safetensors_io import write_safetensors
     typed = ZepavikConfig.from_dict(raw_config)
+    if sharpen is None:
+        sharpen = (2304.0 / typed.width) ** 0.5           # 0.05^2 * sharpen^2 * width = 5.76
     tensors = random_tensors(expected_tensors(zepavik_spec(typed)), seed, std=0.05, dtype=torch.float32)
     for name in tensors:
         if name.endswith((".mix.q", ".mix.k")):
