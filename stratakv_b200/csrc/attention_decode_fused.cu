@@ -116,13 +116,28 @@ __device__ __forceinline__ uint32_t f_pack(float lo, float hi) {
     return *(const uint32_t*)&v;
 }
 
+// What a design may want done to the new token's queries, key and value before they are used and cached: biases
+// (float, [heads * head_dim], [kv_heads * head_dim] twice; null: none) and, with value_norm, each value head divided
+// by sqrt(mean(v^2) + value_eps).  row_stride: floats from one token's row of qkv to the next (a row may hold more
+// than the queries, keys and values).
+struct NewTokenFinish {
+    const float* q_bias; const float* k_bias; const float* v_bias;
+    int value_norm; float value_eps; int row_stride;
+};
+
+__device__ __forceinline__ float4 f_add4(float4 a, const float* bias) {
+    const float4 b = *(const float4*)bias;
+    return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+
 __global__ void __launch_bounds__(FTHREADS, FHD <= 64 ? 2 : 1)
 decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __restrict__ cos_sin,
                               __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                               const int* __restrict__ block_table, int table_width,
                               const int* __restrict__ ctx_after, __nv_bfloat16* __restrict__ out, int num_heads,
                               int num_kv_heads, int block_size, float scale, int window, int splits, int m_tiles,
-                              int write_kv, int block_shift, int stages) {
+                              int write_kv, int block_shift, int stages, const NewTokenFinish finish,
+                              const AttentionExtras extras) {
     extern __shared__ __align__(128) unsigned char fused_smem[];
     constexpr int HALF = FHD / 2;
     pdl_launch_dependents();
@@ -151,7 +166,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     const int my_end = min(end_group, my_first + per_split);
     const int n_chunks = my_end > my_first ? (my_end - my_first + FWARPS - 1) / FWARPS : 0;
     const float scale_log2 = scale * 1.4426950408889634f;
-    const float* token = qkv + (size_t)seq * (q_dim + 2 * kv_dim);
+    const float* token = qkv + (size_t)seq * finish.row_stride;
     const int newest_group = pos >> 4;
     const bool owns_newest = newest_group >= my_first && newest_group < my_end;
 
@@ -211,7 +226,10 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
         for (int i = threadIdx.x; i < items; i += FTHREADS) {
             const int item = i / (HALF / 4), quad = i - item * (HALF / 4);
             const float* x = item < rows ? token + (size_t)(head0 + item) * FHD : token + q_dim + (size_t)kv_head * FHD;
-            const float4 a = *(const float4*)(x + 4 * quad), b = *(const float4*)(x + HALF + 4 * quad);
+            const float* x_bias = item < rows ? (finish.q_bias ? finish.q_bias + (size_t)(head0 + item) * FHD : nullptr)
+                                              : (finish.k_bias ? finish.k_bias + (size_t)kv_head * FHD : nullptr);
+            float4 a = *(const float4*)(x + 4 * quad), b = *(const float4*)(x + HALF + 4 * quad);
+            if (x_bias) { a = f_add4(a, x_bias + 4 * quad); b = f_add4(b, x_bias + HALF + 4 * quad); }
             const float xa[4] = {a.x, a.y, a.z, a.w}, xb[4] = {b.x, b.y, b.z, b.w};
             float first[4], second[4];
 #pragma unroll
@@ -230,14 +248,32 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                 *(uint2*)(k_cache + new_at + HALF + 4 * quad) = high;
             }
         }
-        if (owns_newest) {
+        if (owns_newest && write_kv && finish.value_norm) {
+            // the new value row divided by its root mean square: the first warp holds the row (the launcher
+            // admits head sizes up to 128 here), four numbers a lane
+            if (warp == 0) {
+                float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (lane < FHD / 4) {
+                    v = *(const float4*)(token + q_dim + kv_dim + (size_t)kv_head * FHD + 4 * lane);
+                    if (finish.v_bias) v = f_add4(v, finish.v_bias + (size_t)kv_head * FHD + 4 * lane);
+                }
+                const float squares = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+                const float inverse = 1.0f / sqrtf(squares / (float)FHD + finish.value_eps);
+                if (lane < FHD / 4) {
+                    const uint2 packed = make_uint2(f_pack(v.x * inverse, v.y * inverse), f_pack(v.z * inverse, v.w * inverse));
+                    *(uint2*)(v_cache + new_at + 4 * lane) = packed;
+                    *(uint2*)(fused_smem + F_NEW_AT + FQROW + 8 * lane) = packed;
+                }
+            }
+        } else if (owns_newest) {
             // the new value row (not rotated); or, for a layer that reads a cache which another layer of this
             // step has written, that row and its key as they now stand in the cache
             for (int i = threadIdx.x; i < (write_kv ? 1 : 2) * (FHD / 4); i += FTHREADS) {
                 const int which = write_kv ? 1 : i / (FHD / 4), quad = i % (FHD / 4);
                 uint2 packed;
                 if (write_kv) {
-                    const float4 v = *(const float4*)(token + q_dim + kv_dim + (size_t)kv_head * FHD + 4 * quad);
+                    float4 v = *(const float4*)(token + q_dim + kv_dim + (size_t)kv_head * FHD + 4 * quad);
+                    if (finish.v_bias) v = f_add4(v, finish.v_bias + (size_t)kv_head * FHD + 4 * quad);
                     packed = make_uint2(f_pack(v.x, v.y), f_pack(v.z, v.w));
                     *(uint2*)(v_cache + new_at + 4 * quad) = packed;
                 } else {
@@ -298,7 +334,10 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int key = j0 + 8 * t + 2 * tig + (e & 1);
-                    const float v = (key < ctx && key >= lo) ? s[t][e] * scale_log2 : -INFINITY;
+                    float v = (key < ctx && key >= lo) ? s[t][e] * scale_log2 : -INFINITY;
+                    if (extras.bias && key < ctx && key >= lo && g + 8 * (e >> 1) < rows)
+                        v = fmaf(-1.4426950408889634f,
+                                 __ldg(extras.bias + (size_t)(head0 + g + 8 * (e >> 1)) * extras.bias_len + min(pos - key, extras.bias_len - 1)), v);
                     s[t][e] = v;
                     tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
                 }
@@ -409,7 +448,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
             total += weight * slots[b * FPITCH + d];
             sum += weight * slots[b * FPITCH + FHD + 1];
         }
-        out[((size_t)seq * num_heads + head0 + r) * FHD + d] = __float2bfloat16_rn(total / sum);
+        out[((size_t)seq * num_heads + head0 + r) * FHD + d] = __float2bfloat16_rn(total / sum * gate_factor(extras, seq, head0 + r));
     }
 }
 
@@ -420,12 +459,28 @@ using namespace skv;
 // qkv: float [n_seqs, (heads + 2 kv_heads) * head_dim] (the q|k|v projection of each sequence's new
 // token); cos_sin: float [positions, head_dim/2, 2] or null; ctx_after[s]: keys cached for sequence s
 // once this token's key is in (so the token's position is ctx_after[s] - 1).  splits is 1..8.
-SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin, void* k_cache, void* v_cache,
-                                          const int* block_table, int table_width, const int* ctx_after,
-                                          void* out, int n_seqs, int num_heads, int num_kv_heads, int head_dim,
-                                          int block_size, float scale, int window, int splits, int write_kv,
-                                          cudaStream_t stream) {
+// The _extras form: rows of qkv are row_stride floats apart (0: exactly queries, keys and values); biases, the
+// value norm (value_norm != 0, head sizes up to 128), a bias table by distance and a gate as NewTokenFinish and
+// AttentionExtras say, each off when null or 0.
+SKV_EXPORT int skv_attention_decode_fused_extras(const float* qkv, int row_stride, const float* cos_sin, void* k_cache,
+                                                 void* v_cache, const int* block_table, int table_width,
+                                                 const int* ctx_after, void* out, int n_seqs, int num_heads,
+                                                 int num_kv_heads, int head_dim, int block_size, float scale, int window,
+                                                 int splits, int write_kv, const float* q_bias, const float* k_bias,
+                                                 const float* v_bias, int value_norm, float value_eps, const float* bias,
+                                                 int bias_len, const float* gate, int gate_stride, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
+    const int row_floats = (num_heads + 2 * num_kv_heads) * head_dim;
+    if (row_stride == 0) row_stride = row_floats;
+    if (row_stride < row_floats || row_stride % 4 != 0)
+        return fail("skv_attention_decode_fused", "a row of qkv must hold its queries, keys and values and be a multiple of 16 bytes");
+    if (value_norm && head_dim > 128) return fail("skv_attention_decode_fused", "the value norm is built for head sizes up to 128");
+    if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads))
+        return fail("skv_attention_decode_fused", "a bias table needs its length and a gate rows of at least heads numbers");
+    if (((uintptr_t)q_bias | (uintptr_t)k_bias | (uintptr_t)v_bias) & 15)
+        return fail("skv_attention_decode_fused", "biases must be 16-byte aligned");
+    const NewTokenFinish finish = {q_bias, k_bias, v_bias, value_norm, value_eps, row_stride};
+    const AttentionExtras extras = {bias, bias_len, gate, gate_stride};
     if (head_dim != FHD) return fail("skv_attention_decode_fused", "this library was built for another head size");
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_decode_fused", "heads must be a positive multiple of kv heads");
@@ -478,9 +533,19 @@ SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin
     const cudaError_t status = cudaLaunchKernelEx(
         &config, decode_attention_fused_kernel, qkv, (const float2*)cos_sin, (__nv_bfloat16*)k_cache,
         (__nv_bfloat16*)v_cache, block_table, table_width, ctx_after, (__nv_bfloat16*)out, num_heads, num_kv_heads,
-        block_size, scale, window, splits, m_tiles, write_kv, block_shift, stages);
+        block_size, scale, window, splits, m_tiles, write_kv, block_shift, stages, finish, extras);
     if (status != cudaSuccess) return fail("skv_attention_decode_fused", cudaGetErrorString(status));
     return 0;
+}
+
+SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin, void* k_cache, void* v_cache,
+                                          const int* block_table, int table_width, const int* ctx_after,
+                                          void* out, int n_seqs, int num_heads, int num_kv_heads, int head_dim,
+                                          int block_size, float scale, int window, int splits, int write_kv,
+                                          cudaStream_t stream) {
+    return skv_attention_decode_fused_extras(qkv, 0, cos_sin, k_cache, v_cache, block_table, table_width, ctx_after, out,
+                                             n_seqs, num_heads, num_kv_heads, head_dim, block_size, scale, window, splits,
+                                             write_kv, nullptr, nullptr, nullptr, 0, 0.0f, nullptr, 0, nullptr, 0, stream);
 }
 
 SKV_EXPORT int skv_has_attention_decode_fused() { return 1; }
@@ -489,6 +554,14 @@ SKV_EXPORT int skv_has_attention_decode_fused() { return 1; }
 
 SKV_EXPORT int skv_attention_decode_fused(const float*, const float*, void*, void*, const int*, int, const int*, void*,
                                           int, int, int, int, int, float, int, int, int, cudaStream_t) {
+    return skv::fail("skv_attention_decode_fused",
+                     "this kernel exists in the bfloat16 build for head sizes up to 192 only");
+}
+
+SKV_EXPORT int skv_attention_decode_fused_extras(const float*, int, const float*, void*, void*, const int*, int, const int*,
+                                                 void*, int, int, int, int, int, float, int, int, int, const float*,
+                                                 const float*, const float*, int, float, const float*, int, const float*,
+                                                 int, cudaStream_t) {
     return skv::fail("skv_attention_decode_fused",
                      "this kernel exists in the bfloat16 build for head sizes up to 192 only");
 }

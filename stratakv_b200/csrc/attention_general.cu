@@ -4,7 +4,8 @@
 // distance, and a gate per head on the output.  Two kernels:
 //
 //   qkv_finish:        float rows [q | k | v | ...] of the fused projection -> queries in the compute
-//                      dtype, keys and (normalised) values in their places of the paged cache;
+//                      dtype, keys and (normalised) values in their places of the paged cache; a warp per
+//                      (token, head);
 //   attention_general: one warp per (token, head) over the sequence's own cached keys, online softmax
 //                      by chunks of 32 keys, everything after the loads in float.
 //
@@ -23,53 +24,80 @@ constexpr int GEN_WARPS = 4;
 constexpr int GEN_MAX_VDIM = 256;                 // a lane keeps vdim / 32 accumulators
 constexpr int GEN_ACC = GEN_MAX_VDIM / 32;
 
-// One token per block.  Per head: value_norm != 0 divides each value head by sqrt(mean(v^2) + eps).
-template <typename T>
-__global__ void __launch_bounds__(128)
+// out[i] = (x[i] + bias[i]) * factor for one head of n numbers, by one warp; four numbers a lane where VEC.
+template <typename T, bool VEC>
+__device__ __forceinline__ void finish_head(const float* __restrict__ x, const float* __restrict__ bias,
+                                            T* __restrict__ out, int n, float factor, int lane) {
+    if (VEC) {
+        for (int i = 4 * lane; i < n; i += 128) {
+            float4 v = *(const float4*)(x + i);
+            if (bias) {
+                const float4 b = *(const float4*)(bias + i);
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+            }
+            if (sizeof(T) == 4) {
+                *(float4*)(out + i) = make_float4(v.x * factor, v.y * factor, v.z * factor, v.w * factor);
+            } else {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * factor, v.y * factor);
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * factor, v.w * factor);
+                *(uint2*)(out + i) = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) out[i] = from_float<T>((x[i] + (bias ? bias[i] : 0.0f)) * factor);
+    }
+}
+
+constexpr int FINISH_WARPS = 8;
+
+// One warp per (token, head): the token's query heads, then its key heads, then its value heads.
+// value_norm != 0 divides each value head by sqrt(mean(v^2) + eps).  VEC: head sizes and the row stride are
+// multiples of 4 and every pointer is 16-byte aligned.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(FINISH_WARPS * 32)
 qkv_finish_kernel(const float* __restrict__ qkv, int row_stride, const float* __restrict__ q_bias,
                   const float* __restrict__ k_bias, const float* __restrict__ v_bias,
                   const int* __restrict__ positions, const int* __restrict__ token_seq,
                   const int* __restrict__ block_table, int table_width, T* __restrict__ q_out,
-                  T* __restrict__ k_cache, T* __restrict__ v_cache, int num_heads, int num_kv_heads, int dim,
-                  int vdim, int block_size, int value_norm, float value_eps, int write_kv) {
+                  T* __restrict__ k_cache, T* __restrict__ v_cache, int n_tokens, int num_heads, int num_kv_heads,
+                  int dim, int vdim, int block_size, int value_norm, float value_eps, int write_kv) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
-    const int q_width = num_heads * dim, k_width = num_kv_heads * dim, v_width = num_kv_heads * vdim;
+    const int lane = threadIdx.x & 31;
+    const int per_token = num_heads + 2 * num_kv_heads;
+    const long long item = (long long)blockIdx.x * FINISH_WARPS + (threadIdx.x >> 5);
+    if (item >= (long long)n_tokens * per_token) return;        // whole warps leave together
+    const int t = (int)(item / per_token), which = (int)(item - (long long)t * per_token);
     const float* src = qkv + (size_t)t * row_stride;
-    T* q_row = q_out + (size_t)t * q_width;
-    for (int c = threadIdx.x; c < q_width; c += blockDim.x)
-        q_row[c] = from_float<T>(src[c] + (q_bias ? q_bias[c] : 0.0f));
+    if (which < num_heads) {
+        finish_head<T, VEC>(src + (size_t)which * dim, q_bias ? q_bias + (size_t)which * dim : nullptr,
+                            q_out + ((size_t)t * num_heads + which) * dim, dim, 1.0f, lane);
+        return;
+    }
     if (!write_kv) return;
     const int pos = positions[t];
     const int block = block_table[(size_t)token_seq[t] * table_width + pos / block_size];
     const size_t tile_row = (size_t)block * num_kv_heads * block_size + (pos % block_size);   // of kv head 0
-    const float* k_src = src + q_width;
-    for (int c = threadIdx.x; c < k_width; c += blockDim.x) {
-        const int g = c / dim, d = c - g * dim;
-        k_cache[(tile_row + (size_t)g * block_size) * dim + d] = from_float<T>(k_src[c] + (k_bias ? k_bias[c] : 0.0f));
-    }
-    const float* v_src = k_src + k_width;
-    if (!value_norm) {
-        for (int c = threadIdx.x; c < v_width; c += blockDim.x) {
-            const int g = c / vdim, d = c - g * vdim;
-            v_cache[(tile_row + (size_t)g * block_size) * vdim + d] = from_float<T>(v_src[c] + (v_bias ? v_bias[c] : 0.0f));
-        }
+    const int q_width = num_heads * dim, k_width = num_kv_heads * dim;
+    if (which < num_heads + num_kv_heads) {
+        const int g = which - num_heads;
+        finish_head<T, VEC>(src + q_width + (size_t)g * dim, k_bias ? k_bias + (size_t)g * dim : nullptr,
+                            k_cache + (tile_row + (size_t)g * block_size) * dim, dim, 1.0f, lane);
         return;
     }
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int g = warp; g < num_kv_heads; g += warps) {
-        const float* head = v_src + (size_t)g * vdim;
-        const float* bias = v_bias ? v_bias + (size_t)g * vdim : nullptr;
+    const int g = which - num_heads - num_kv_heads;
+    const float* head = src + q_width + k_width + (size_t)g * vdim;
+    const float* bias = v_bias ? v_bias + (size_t)g * vdim : nullptr;
+    float factor = 1.0f;
+    if (value_norm) {
         float squares = 0.0f;
         for (int d = lane; d < vdim; d += 32) {
             const float v = head[d] + (bias ? bias[d] : 0.0f);
             squares = fmaf(v, v, squares);
         }
-        const float inverse = 1.0f / sqrtf(warp_sum(squares) / (float)vdim + value_eps);
-        T* dst = v_cache + (tile_row + (size_t)g * block_size) * vdim;
-        for (int d = lane; d < vdim; d += 32) dst[d] = from_float<T>((head[d] + (bias ? bias[d] : 0.0f)) * inverse);
+        factor = 1.0f / sqrtf(warp_sum(squares) / (float)vdim + value_eps);
     }
+    finish_head<T, VEC>(head, bias, v_cache + (tile_row + (size_t)g * block_size) * vdim, vdim, factor, lane);
 }
 
 __device__ __forceinline__ float general_dot(const float* __restrict__ q, const float* __restrict__ row, int dim) {
@@ -195,9 +223,16 @@ SKV_EXPORT int skv_qkv_finish(const float* qkv, int row_stride, const float* q_b
         return fail("skv_qkv_finish", "head counts, head sizes and block_size must be positive");
     if (row_stride < (num_heads + num_kv_heads) * dim + num_kv_heads * vdim)
         return fail("skv_qkv_finish", "a row is shorter than its queries, keys and values");
-    return launch_pdl("skv_qkv_finish", qkv_finish_kernel<skv_t>, dim3(n_tokens), dim3(128), 0, stream, qkv,
+    const long long items = (long long)n_tokens * (num_heads + 2 * num_kv_heads);
+    const long long blocks = (items + FINISH_WARPS - 1) / FINISH_WARPS;
+    if (blocks > 0x7fffffffLL) return fail("skv_qkv_finish", "too many tokens in one step");
+    const bool vec = dim % 4 == 0 && vdim % 4 == 0 && row_stride % 4 == 0 &&
+                     (((uintptr_t)qkv | (uintptr_t)q_bias | (uintptr_t)k_bias | (uintptr_t)v_bias | (uintptr_t)q_out |
+                       (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;
+    auto kernel = vec ? qkv_finish_kernel<skv_t, true> : qkv_finish_kernel<skv_t, false>;
+    return launch_pdl("skv_qkv_finish", kernel, dim3((unsigned)blocks), dim3(FINISH_WARPS * 32), 0, stream, qkv,
                       row_stride, q_bias, k_bias, v_bias, positions, token_seq, block_table, table_width,
-                      (skv_t*)q_out, (skv_t*)k_cache, (skv_t*)v_cache, num_heads, num_kv_heads, dim, vdim,
+                      (skv_t*)q_out, (skv_t*)k_cache, (skv_t*)v_cache, n_tokens, num_heads, num_kv_heads, dim, vdim,
                       block_size, value_norm, value_eps, write_kv);
 }
 

@@ -362,24 +362,37 @@ class Kernels:
 
     def attention_decode_fused(self, qkv, cos_sin, k_cache, v_cache, block_table, ctx_after, out, num_heads: int,
                                num_kv_heads: int, head_dim: int, block_size: int, scale: float, window: int = 0,
-                               splits: int = 1, write_kv: bool = True):
+                               splits: int = 1, write_kv: bool = True, q_bias=None, k_bias=None, v_bias=None,
+                               value_norm_eps=None, bias=None, gate=None, gate_stride: int = 0):
         """One new token per sequence (bfloat16 build), from the float32 q|k|v projection: rotates queries
         and the new key (``cos_sin`` table, or ``None`` for no rotation), writes the new key and value into
-        the cache, attends over ``ctx_after[s]`` keys and merges ``splits`` (1..8) context pieces in-kernel."""
+        the cache, attends over ``ctx_after[s]`` keys and merges ``splits`` (1..8) context pieces in-kernel.
+        A row of ``qkv`` may be wider than its queries, keys and values.  Optional: float32 biases on the three,
+        each value head divided by its root mean square (``value_norm_eps``), and ``bias``/``gate`` as in
+        ``attention_prefill``."""
         self._want(qkv, torch.float32, "qkv"); self._want(out, self.dtype, "out")
         self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
         self._want(block_table, torch.int32, "block_table"); self._want(ctx_after, torch.int32, "ctx_after")
         if cos_sin is not None:
             self._want(cos_sin, torch.float32, "cos_sin")
         n = qkv.shape[0]
-        if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
-            raise KernelError("attention_decode_fused: qkv width does not match the head counts")
+        if qkv.shape[1] < (num_heads + 2 * num_kv_heads) * head_dim:
+            raise KernelError("attention_decode_fused: a row of qkv is shorter than its queries, keys and values")
         if ctx_after.numel() != n or block_table.shape[0] != n:
             raise KernelError("attention_decode_fused: one length and one table row per sequence is needed")
-        self._check(self.lib.skv_attention_decode_fused(
-            _ptr(qkv), _ptr(cos_sin), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+        for name, vector, width in (("q_bias", q_bias, num_heads * head_dim), ("k_bias", k_bias, num_kv_heads * head_dim),
+                                    ("v_bias", v_bias, num_kv_heads * head_dim)):
+            if vector is not None:
+                self._want(vector, torch.float32, name)
+                if vector.numel() != width:
+                    raise KernelError(f"attention_decode_fused: {name} must hold {width} numbers")
+        self._check(self.lib.skv_attention_decode_fused_extras(
+            _ptr(qkv), qkv.shape[1], _ptr(cos_sin), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
             _ptr(ctx_after), _ptr(out), n, num_heads, num_kv_heads, head_dim, block_size, ctypes.c_float(scale),
-            window, splits, int(bool(write_kv)), _stream()), "attention_decode_fused")
+            window, splits, int(bool(write_kv)), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
+            int(value_norm_eps is not None), ctypes.c_float(value_norm_eps or 0.0),
+            *self._extras(bias, gate, gate_stride, num_heads, "attention_decode_fused"), _stream()),
+            "attention_decode_fused")
 
     def embed_sum(self, table, ids, out, positions, token_seq, cu_q, slot_ids, flag=None, pair_table=None,
                   last_ids=None, mul_prev: int = 0, mul_cur: int = 0, position_table=None,

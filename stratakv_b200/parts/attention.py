@@ -164,9 +164,14 @@ class PagedAttention(Mixer):
         n = h.shape[0]
         fused = rt.workspace.get("qkv", (n, self.fused_width), torch.float32)
         ops.linear(h, self.w_qkv, fused, _ops.MODE_STORE_F32)
-        q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
         k_cache, v_cache = step.cache.entry_kv(cache_entry)
         table = step.block_tables[step.cache.entry_group_index(cache_entry)]
+        if step.is_decode and self._specialised():
+            ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
+            if self._decode_fused(step, fused, ctx, k_cache, v_cache, table, writes_cache):
+                ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
+                return
+        q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
         ops.qkv_finish(fused, q, k_cache, v_cache, step.positions, step.token_seq, table, s.num_heads,
                        s.num_kv_heads, s.head_dim, s.value_dim, step.cache.block_size, self.q_bias, self.k_bias,
                        self.v_bias, s.value_norm_eps, writes_cache)
@@ -179,6 +184,28 @@ class PagedAttention(Mixer):
                               s.num_kv_heads, s.head_dim, s.value_dim, step.cache.block_size, s.scale, s.window,
                               self.r1, self.r2, gate, self.fused_width)
         ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
+
+    def _decode_fused(self, step, fused, ctx, k_cache, v_cache, table, writes_cache) -> bool:
+        """One token a sequence, in one kernel straight from the fused projection: biases, value norm, cache write,
+        attention with the bias table over up to 8 pieces of the context, their merge, the gate.  False where
+        that kernel does not serve (then ``qkv_finish`` and the split kernel do)."""
+        s, rt = self.spec, self.rt
+        ops = rt.kernels(s.head_dim)
+        block_size = step.cache.block_size
+        if not ops.has_attention_decode_fused() or s.head_dim > 128 or block_size % 16 != 0:
+            return False
+        n = fused.shape[0]
+        blocks_per_seq = s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16))
+        keys = min(step.max_ctx, s.window) if s.window > 0 else step.max_ctx
+        splits = fused_decode_splits(n, blocks_per_seq, keys, rt.sm_count, per_sm=2 if s.head_dim <= 64 else 1)
+        if wants_more_pieces(n, blocks_per_seq, keys, splits, rt.sm_count):
+            return False
+        ops.attention_decode_fused(fused, None, k_cache, v_cache, table, step.ctx_after, ctx, s.num_heads, s.num_kv_heads,
+                                   s.head_dim, block_size, s.scale, s.window, splits, writes_cache,
+                                   q_bias=self.q_bias, k_bias=self.k_bias, v_bias=self.v_bias,
+                                   value_norm_eps=s.value_norm_eps, bias=self.bias_table,
+                                   gate=fused[:, self.gate_offset:] if s.gate_weight else None, gate_stride=self.fused_width)
+        return True
 
     def _attend_specialised(self, step, q, ctx, k_cache, v_cache, table, gate) -> bool:
         """Attention through the kernels of the head size's own library, which take the distance bias as a table and

@@ -268,6 +268,53 @@ def test_attention_kernels_of_one_head_size_take_the_bias_and_the_gate(window, h
         np.testing.assert_allclose(out.double().cpu().numpy(), want, err_msg=f"decode in {splits}", **tol)
 
 
+@pytest.mark.parametrize("window", [0, 24, 100])
+@pytest.mark.parametrize("heads,kv_heads,dim", [(4, 2, 16), (2, 2, 64), (8, 1, 32), (20, 1, 64), (2, 1, 128)])
+def test_fused_decode_finishes_the_new_token_itself(window, heads, kv_heads, dim):
+    """Straight from the float32 rows [q | k | v | gate]: biases, the value norm, the cache write of the new token,
+    attention with the bias table in one piece and in four, the gate."""
+    dtype = torch.bfloat16
+    ops = kernels(dtype, dim)
+    assert ops.has_attention_decode_fused()
+    g = torch.Generator().manual_seed(5)
+    r1 = (torch.rand(heads, generator=g) + 0.1).cuda()
+    r2 = (torch.rand(heads, generator=g) * 2 + 0.05).cuda()
+    lengths = [300, 1, 70, 129, 25]
+    scene = Scene(dtype, lengths, [1] * 5, heads, kv_heads, dim, dim, 64, seed=dim + window + 2,
+                  loud=[(0, d) for _, d in LOUD[2:]])
+    biases = [torch.randn(heads * dim, generator=g), torch.randn(kv_heads * dim, generator=g), torch.randn(kv_heads * dim, generator=g)]
+    stride = -(-((heads + 2 * kv_heads) * dim + heads) // 8) * 8
+    rows = torch.zeros(5, stride)
+    eps = 1e-3
+    for s, length in enumerate(lengths):
+        last = length - 1
+        raw_v = torch.randn(kv_heads, dim, generator=g) * 2
+        finished_v = plain_zepavik.rms_divide(raw_v.double() + biases[2].double().view(kv_heads, dim), eps)
+        scene.v[s][last] = finished_v.to(dtype)
+        rows[s, :heads * dim] = scene.q[s][last].float().reshape(-1) - biases[0]
+        rows[s, heads * dim:(heads + kv_heads) * dim] = scene.k[s][last].float().reshape(-1) - biases[1]
+        rows[s, (heads + kv_heads) * dim:(heads + 2 * kv_heads) * dim] = raw_v.reshape(-1)
+        page, row = scene.tables[s][last // 64], last % 64
+        scene.k_cache[page, :, row] = 30.0                     # the new token is not in the cache yet
+        scene.v_cache[page, :, row] = 1000.0
+    gate_at = (heads + 2 * kv_heads) * dim
+    rows[:, gate_at:gate_at + heads] = torch.randn(5, heads, generator=g)
+    rows = rows.cuda()
+    table = bias_table(r1, r2, window or 300)
+    want = scene.plain(0.3, window, r1, r2, rows[:, gate_at:gate_at + heads])
+    for splits in (1, 4):
+        out = torch.zeros((5, heads * dim), dtype=dtype, device="cuda")
+        ops.attention_decode_fused(rows, None, scene.k_cache, scene.v_cache, scene.table, scene.ctx_after, out, heads,
+                                   kv_heads, dim, 64, 0.3, window, splits, True, q_bias=biases[0].cuda(),
+                                   k_bias=biases[1].cuda(), v_bias=biases[2].cuda(), value_norm_eps=eps, bias=table,
+                                   gate=rows[:, gate_at:], gate_stride=stride)
+        np.testing.assert_allclose(out.double().cpu().numpy(), want, err_msg=f"fused decode in {splits}", rtol=2e-2, atol=2e-2)
+        for s, length in enumerate(lengths):
+            page, row = scene.tables[s][(length - 1) // 64], (length - 1) % 64
+            np.testing.assert_allclose(scene.k_cache[page, :, row].double().cpu().numpy(), scene.k[s][length - 1].double().numpy(), rtol=1e-2, atol=1e-2)
+            np.testing.assert_allclose(scene.v_cache[page, :, row].double().cpu().numpy(), scene.v[s][length - 1].double().numpy(), rtol=1e-2, atol=1e-2)
+
+
 # ---- the projection that stores an activation ----------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rows", [1, 7, 16, 40, 128, 300])
