@@ -24,35 +24,32 @@ constexpr int GEN_WARPS = 4;
 constexpr int GEN_MAX_VDIM = 256;                 // a lane keeps vdim / 32 accumulators
 constexpr int GEN_ACC = GEN_MAX_VDIM / 32;
 
-// out[i] = (x[i] + bias[i]) * factor for one head of n numbers, by one warp; four numbers a lane where VEC.
-template <typename T, bool VEC>
-__device__ __forceinline__ void finish_head(const float* __restrict__ x, const float* __restrict__ bias,
-                                            T* __restrict__ out, int n, float factor, int lane) {
-    if (VEC) {
-        for (int i = 4 * lane; i < n; i += 128) {
-            float4 v = *(const float4*)(x + i);
-            if (bias) {
-                const float4 b = *(const float4*)(bias + i);
-                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-            }
-            if (sizeof(T) == 4) {
-                *(float4*)(out + i) = make_float4(v.x * factor, v.y * factor, v.z * factor, v.w * factor);
-            } else {
-                const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * factor, v.y * factor);
-                const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * factor, v.w * factor);
-                *(uint2*)(out + i) = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
-            }
-        }
+constexpr int FINISH_WARPS = 8;
+
+template <typename T>
+__device__ __forceinline__ void finish_store4(T* out, float4 v, float factor) {
+    if (sizeof(T) == 4) {
+        *(float4*)out = make_float4(v.x * factor, v.y * factor, v.z * factor, v.w * factor);
     } else {
-        for (int i = lane; i < n; i += 32) out[i] = from_float<T>((x[i] + (bias ? bias[i] : 0.0f)) * factor);
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * factor, v.y * factor);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * factor, v.w * factor);
+        *(uint2*)out = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
     }
 }
 
-constexpr int FINISH_WARPS = 8;
+__device__ __forceinline__ float4 finish_load4(const float* x, const float* bias) {
+    float4 v = *(const float4*)x;
+    if (bias) {
+        const float4 b = *(const float4*)bias;
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+    }
+    return v;
+}
 
 // One warp per (token, head): the token's query heads, then its key heads, then its value heads.
-// value_norm != 0 divides each value head by sqrt(mean(v^2) + eps).  VEC: head sizes and the row stride are
-// multiples of 4 and every pointer is 16-byte aligned.
+// value_norm != 0 divides each value head by sqrt(mean(v^2) + eps).  VEC: head sizes (at most 256) and the row
+// stride are multiples of 4 and every pointer is 16-byte aligned; a lane then holds up to eight numbers of the
+// head, whose loads go out before the lookups that say where the head is to be written.
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(FINISH_WARPS * 32)
 qkv_finish_kernel(const float* __restrict__ qkv, int row_stride, const float* __restrict__ q_bias,
@@ -68,36 +65,59 @@ qkv_finish_kernel(const float* __restrict__ qkv, int row_stride, const float* __
     const long long item = (long long)blockIdx.x * FINISH_WARPS + (threadIdx.x >> 5);
     if (item >= (long long)n_tokens * per_token) return;        // whole warps leave together
     const int t = (int)(item / per_token), which = (int)(item - (long long)t * per_token);
-    const float* src = qkv + (size_t)t * row_stride;
-    if (which < num_heads) {
-        finish_head<T, VEC>(src + (size_t)which * dim, q_bias ? q_bias + (size_t)which * dim : nullptr,
-                            q_out + ((size_t)t * num_heads + which) * dim, dim, 1.0f, lane);
-        return;
+    const bool is_query = which < num_heads, is_key = !is_query && which < num_heads + num_kv_heads;
+    if (!is_query && !write_kv) return;
+    const int g = is_query ? which : (is_key ? which - num_heads : which - num_heads - num_kv_heads);
+    const int n = is_query || is_key ? dim : vdim;
+    const float* x = qkv + (size_t)t * row_stride + (is_query ? (size_t)g * dim
+                     : is_key ? (size_t)num_heads * dim + (size_t)g * dim
+                              : (size_t)(num_heads + num_kv_heads) * dim + (size_t)g * vdim);
+    const float* bias_base = is_query ? q_bias : (is_key ? k_bias : v_bias);
+    const float* bias = bias_base ? bias_base + (size_t)g * n : nullptr;
+    const bool normed = !is_query && !is_key && value_norm;
+
+    float4 held[2];
+    if (VEC) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int i = 4 * lane + 128 * u;
+            held[u] = i < n ? finish_load4(x + i, bias ? bias + i : nullptr) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
     }
-    if (!write_kv) return;
-    const int pos = positions[t];
-    const int block = block_table[(size_t)token_seq[t] * table_width + pos / block_size];
-    const size_t tile_row = (size_t)block * num_kv_heads * block_size + (pos % block_size);   // of kv head 0
-    const int q_width = num_heads * dim, k_width = num_kv_heads * dim;
-    if (which < num_heads + num_kv_heads) {
-        const int g = which - num_heads;
-        finish_head<T, VEC>(src + q_width + (size_t)g * dim, k_bias ? k_bias + (size_t)g * dim : nullptr,
-                            k_cache + (tile_row + (size_t)g * block_size) * dim, dim, 1.0f, lane);
-        return;
+    T* out;
+    if (is_query) {
+        out = q_out + ((size_t)t * num_heads + g) * dim;
+    } else {
+        const int pos = positions[t];
+        const int block = block_table[(size_t)token_seq[t] * table_width + pos / block_size];
+        const size_t row = ((size_t)block * num_kv_heads + g) * block_size + (pos % block_size);
+        out = (is_key ? k_cache : v_cache) + row * n;
     }
-    const int g = which - num_heads - num_kv_heads;
-    const float* head = src + q_width + k_width + (size_t)g * vdim;
-    const float* bias = v_bias ? v_bias + (size_t)g * vdim : nullptr;
     float factor = 1.0f;
-    if (value_norm) {
+    if (VEC) {
+        if (normed) {
+            float squares = 0.0f;
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                squares += held[u].x * held[u].x + held[u].y * held[u].y + held[u].z * held[u].z + held[u].w * held[u].w;
+            factor = 1.0f / sqrtf(warp_sum(squares) / (float)n + value_eps);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int i = 4 * lane + 128 * u;
+            if (i < n) finish_store4<T>(out + i, held[u], factor);
+        }
+        return;
+    }
+    if (normed) {
         float squares = 0.0f;
-        for (int d = lane; d < vdim; d += 32) {
-            const float v = head[d] + (bias ? bias[d] : 0.0f);
+        for (int d = lane; d < n; d += 32) {
+            const float v = x[d] + (bias ? bias[d] : 0.0f);
             squares = fmaf(v, v, squares);
         }
-        factor = 1.0f / sqrtf(warp_sum(squares) / (float)vdim + value_eps);
+        factor = 1.0f / sqrtf(warp_sum(squares) / (float)n + value_eps);
     }
-    finish_head<T, VEC>(head, bias, v_cache + (tile_row + (size_t)g * block_size) * vdim, vdim, factor, lane);
+    for (int d = lane; d < n; d += 32) out[d] = from_float<T>((x[d] + (bias ? bias[d] : 0.0f)) * factor);
 }
 
 __device__ __forceinline__ float general_dot(const float* __restrict__ q, const float* __restrict__ row, int dim) {
@@ -226,7 +246,7 @@ SKV_EXPORT int skv_qkv_finish(const float* qkv, int row_stride, const float* q_b
     const long long items = (long long)n_tokens * (num_heads + 2 * num_kv_heads);
     const long long blocks = (items + FINISH_WARPS - 1) / FINISH_WARPS;
     if (blocks > 0x7fffffffLL) return fail("skv_qkv_finish", "too many tokens in one step");
-    const bool vec = dim % 4 == 0 && vdim % 4 == 0 && row_stride % 4 == 0 &&
+    const bool vec = dim % 4 == 0 && vdim % 4 == 0 && dim <= 256 && vdim <= 256 && row_stride % 4 == 0 &&
                      (((uintptr_t)qkv | (uintptr_t)q_bias | (uintptr_t)k_bias | (uintptr_t)v_bias | (uintptr_t)q_out |
                        (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;
     auto kernel = vec ? qkv_finish_kernel<skv_t, true> : qkv_finish_kernel<skv_t, false>;
