@@ -140,8 +140,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                 const int key = j0 + 8 * t + 2 * tig + (c & 1);
                 float v = (key < ctx && key >= lo) ? s[t][c] * scale_log2 : -INFINITY;
                 if (extras.bias && key < ctx && key >= lo && g + 8 * (c >> 1) < rows)
-                    v = fmaf(-1.4426950408889634f,
-                             __ldg(extras.bias + (size_t)(head0 + g + 8 * (c >> 1)) * extras.bias_len + min(ctx - 1 - key, extras.bias_len - 1)), v);
+                    v -= __ldg(extras.bias + (size_t)(head0 + g + 8 * (c >> 1)) * extras.bias_len + min(ctx - 1 - key, extras.bias_len - 1));
                 s[t][c] = v;
                 tile_max[c >> 1] = fmaxf(tile_max[c >> 1], v);
             }

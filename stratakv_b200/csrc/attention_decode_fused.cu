@@ -336,8 +336,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                     const int key = j0 + 8 * t + 2 * tig + (e & 1);
                     float v = (key < ctx && key >= lo) ? s[t][e] * scale_log2 : -INFINITY;
                     if (extras.bias && key < ctx && key >= lo && g + 8 * (e >> 1) < rows)
-                        v = fmaf(-1.4426950408889634f,
-                                 __ldg(extras.bias + (size_t)(head0 + g + 8 * (e >> 1)) * extras.bias_len + min(pos - key, extras.bias_len - 1)), v);
+                        v -= __ldg(extras.bias + (size_t)(head0 + g + 8 * (e >> 1)) * extras.bias_len + min(pos - key, extras.bias_len - 1));
                     s[t][e] = v;
                     tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
                 }

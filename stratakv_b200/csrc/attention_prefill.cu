@@ -169,7 +169,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                     const int pos = (c >> 1) ? pos_bottom : pos_top;
                     const bool seen = key <= pos && (window == 0 || key > pos - window);
                     float v = seen ? s[n][c] * scale_log2 : -INFINITY;
-                    if (bias_row && seen) v = fmaf(-1.4426950408889634f, __ldg(bias_row + min(pos - key, extras.bias_len - 1)), v);
+                    if (bias_row && seen) v -= __ldg(bias_row + min(pos - key, extras.bias_len - 1));
                     s[n][c] = v;
                     tile_max[c >> 1] = fmaxf(tile_max[c >> 1], v);
                 }

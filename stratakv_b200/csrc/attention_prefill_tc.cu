@@ -342,10 +342,18 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
             if (bias_row) {
+                const int nearest = pos - key0 - (ABN - 1);            // the distance of the tile's last key
+                if (nearest >= 0 && pos - key0 < extras.bias_len) {
+                    // every distance of the tile lies inside the table: one load and one multiply-add a score
+                    const float* at = bias_row + (pos - key0);
 #pragma unroll
-                for (int e = 0; e < ABN; ++e) {                        // (a masked score stays -infinity)
-                    const int distance = min(max(pos - key0 - e, 0), extras.bias_len - 1);
-                    sc[e] = fmaf(sc[e], scale_log2, -1.4426950408889634f * __ldg(bias_row + distance));
+                    for (int e = 0; e < ABN; ++e) sc[e] = fmaf(sc[e], scale_log2, -__ldg(at - e));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < ABN; ++e) {                    // (a masked score stays -infinity)
+                        const int distance = min(max(pos - key0 - e, 0), extras.bias_len - 1);
+                        sc[e] = fmaf(sc[e], scale_log2, -__ldg(bias_row + distance));
+                    }
                 }
             }
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};

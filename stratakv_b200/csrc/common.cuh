@@ -136,8 +136,9 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
 
 // Two optional terms of an attention kernel, both off when their pointer is null.
 //   bias:  a table [num_heads][bias_len]; bias[h][d] is taken off the score of a key at distance d from the
-//          query (a distance beyond the table reads its last entry).  Natural units (the kernels that keep their
-//          scores in units of log2 multiply by log2 e).
+//          query (a distance beyond the table reads its last entry).  The entries are in units of log2, that is the
+//          natural bias times log2 e: the kernels that take a table keep their scores so (2^x by the special-function
+//          unit).
 //   gate:  the logit of (token t, head h) at gate[t * gate_stride + h]; the head's output is multiplied by its sigmoid.
 struct AttentionExtras {
     const float* bias;

@@ -170,6 +170,25 @@ __device__ __forceinline__ float gate_activation(float g, int act) {
     return __fdividef(g, 1.0f + __expf(-z));
 }
 
+// The activation of a projection that stores act(a . w^T) (ACT_ON_STORE in `act`), on 32 accumulator values at once:
+// the test sits outside the unrolled loop, so a store without an activation pays one branch per 32 values and one
+// with the square of relu two instructions a value.  silu and the tanh form of gelu are gate_activation's.
+__device__ __forceinline__ float store_activation(float x, int act) {
+    return (act & ACT_ON_STORE) ? gate_activation(x, act & 0xff) : x;
+}
+
+__device__ __forceinline__ void activate_for_store(uint32_t (&v)[32], int act) {
+    if (!(act & ACT_ON_STORE)) return;
+    const int code = act & 0xff;
+    if (code == ACT_RELU2) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(relu_squared(__uint_as_float(v[e])));
+    } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(gate_activation(__uint_as_float(v[e]), code));
+    }
+}
+
 // Which tile of the output a block's t-th tile is.  Row tiles run fastest, so that blocks which run together share a
 // W tile; but with very many tokens the A tiles of one sweep over the rows no longer fit in L2 (39,000 tokens x 4,096
 // x 2 bytes are 320 MB) and every column of tiles would fetch A from memory again.  So the rows are walked in bands:
@@ -219,6 +238,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, in
                 uint32_t v[32];
                 tmem_load_32(lane_base + (uint32_t)(seg * acc_per_slab + sub * 32), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (mode == TC_MODE_STORE) activate_for_store(v, act);
                 if (mode == TC_MODE_GATED) {
                     // 32 accumulator columns = two groups of (8 gate, 8 up) -> 16 outputs = 2 pieces
 #pragma unroll
@@ -242,8 +262,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, in
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const __nv_bfloat162 pair = __floats2bfloat162_rn(
-                                stored_value(__uint_as_float(v[8 * piece + 2 * e]), act),
-                                stored_value(__uint_as_float(v[8 * piece + 2 * e + 1]), act));
+                                __uint_as_float(v[8 * piece + 2 * e]), __uint_as_float(v[8 * piece + 2 * e + 1]));
                             packed[e] = *(const uint32_t*)&pair;
                         }
                         slab_write(slab, lane, sub * 4 + piece, make_uint4(packed[0], packed[1], packed[2], packed[3]));
@@ -275,6 +294,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, in
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             if (m >= M) continue;
             const int n = n0 + c;
+            if (mode == TC_MODE_STORE) activate_for_store(v, act);
             if (mode == TC_MODE_GATED) {
                 // columns come in groups of 16: 8 gate columns, then their 8 up columns
                 const int half_n = N >> 1;
@@ -303,14 +323,14 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, in
                         uint32_t packed[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 pair = __floats2bfloat162_rn(stored_value(__uint_as_float(v[j + 2 * e]), act),
-                                                                              stored_value(__uint_as_float(v[j + 2 * e + 1]), act));
+                            const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * e]),
+                                                                              __uint_as_float(v[j + 2 * e + 1]));
                             packed[e] = *(const uint32_t*)&pair;
                         }
                         *(uint4*)(dst + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     }
                 } else {
-                    for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(stored_value(__uint_as_float(v[j]), act));
+                    for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
                 }
             } else {
                 float* dst = (float*)out + (size_t)m * N + n;
@@ -977,7 +997,7 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
                 if (mode == TC_MODE_STORE) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        if (c + j < M) ((__nv_bfloat16*)out)[(size_t)(c + j) * N + n] = __float2bfloat16_rn(stored_value(__uint_as_float(v[j]), act));
+                        if (c + j < M) ((__nv_bfloat16*)out)[(size_t)(c + j) * N + n] = __float2bfloat16_rn(store_activation(__uint_as_float(v[j]), act));
                 } else if (mode == TC_MODE_STORE_F32) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)

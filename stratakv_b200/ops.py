@@ -296,7 +296,8 @@ class Kernels:
                           window: int = 0, bias=None, gate=None, gate_stride: int = 0):
         """Many new tokens per sequence (bfloat16 build, head size up to 128): sequence ``s`` owns rows
         ``cu_q[s]..cu_q[s+1]-1`` of ``q``/``out``; ``ctx_after[s]`` keys are cached, this step's included.
-        ``bias`` (float32 ``[heads, distances]``): ``bias[h, i - j]`` is taken off the score of query i and key j.
+        ``bias`` (float32 ``[heads, distances]``, in units of log2: the natural bias times log2 e): ``bias[h, i - j]`` is
+        taken off the score of query i and key j.
         ``gate`` (float32 logits, token t and head h at ``[t * gate_stride + h]``): the output times its sigmoid."""
         self._want(q, self.dtype, "q"); self._want(out, self.dtype, "out")
         self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")

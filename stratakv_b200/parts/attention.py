@@ -16,6 +16,8 @@ that carry the bias and the gate (``csrc/attention_general.cu``).
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .. import ops as _ops
@@ -138,14 +140,15 @@ class PagedAttention(Mixer):
         self.r2 = as_float(s.distance_bias.r2) if s.distance_bias else None
         self.bias_table = None
         if s.distance_bias and self._specialised():
-            # what the bias takes off a score, by head and distance, for the kernels that look it up: as far as the
-            # window reaches, or as far as the model's positions do
+            # what the bias takes off a score, by head and distance, for the kernels that look it up (they keep
+            # scores in units of log2, so the table is in those units): as far as the window reaches, or as far as
+            # the model's positions do
             reach = min(s.window or s.distance_bias.max_distance, s.distance_bias.max_distance or s.window)
             if reach > 0:
                 r1 = tensors[s.distance_bias.r1].to(torch.float64)[:, None]
                 r2 = tensors[s.distance_bias.r2].to(torch.float64)[:, None]
                 r1, r2 = r1.cpu(), r2.cpu()         # (random weights may have been drawn on the device)
-                table = r1 * torch.log1p(r2 * torch.arange(reach, dtype=torch.float64)[None, :])
+                table = r1 * torch.log1p(r2 * torch.arange(reach, dtype=torch.float64)[None, :]) * math.log2(math.e)
                 self.bias_table = self.rt.upload(table.to(torch.float32).contiguous(), torch.float32)
 
     def _specialised(self) -> bool:

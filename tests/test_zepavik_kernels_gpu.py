@@ -225,7 +225,8 @@ def test_attention_with_run_time_sizes(dtype, window, heads, kv_heads, dim, vdim
 
 def bias_table(r1, r2, reach):
     distance = torch.arange(reach, dtype=torch.float64)[None, :]
-    return (r1.double().cpu()[:, None] * torch.log1p(r2.double().cpu()[:, None] * distance)).float().cuda()
+    natural = r1.double().cpu()[:, None] * torch.log1p(r2.double().cpu()[:, None] * distance)
+    return (natural * math.log2(math.e)).float().cuda()          # the kernels take it in units of log2
 
 
 @pytest.mark.parametrize("window", [0, 24, 100])
