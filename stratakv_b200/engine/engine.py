@@ -95,12 +95,26 @@ class Engine:
         self._io_bytes = (0, 0)
 
     # ---- construction ----------------------------------------------------------
+    @staticmethod
+    def _servable(spec: ModelSpec, config: EngineConfig, verbose: bool) -> EngineConfig:
+        """The engine configuration a model of this description is served with.  The bfloat16 kernels read rows
+        of 16 bytes, so a model whose width is no multiple of 8 is served by the float32 kernels, which take any
+        size (its weights are widened once at load time)."""
+        if config.dtype == torch.bfloat16 and spec.hidden_size % 8 != 0:
+            if verbose:
+                import sys
+                print(f"[stratakv_b200] width {spec.hidden_size} is no multiple of 8: served in float32", file=sys.stderr)
+            import dataclasses
+            return dataclasses.replace(config, dtype=torch.float32)
+        return config
+
     @classmethod
     def from_folder(cls, model_dir, config: EngineConfig, verbose: bool = True) -> "Engine":
         """Open a folder with ``config.json`` and ``model.safetensors``; the
         architecture named in ``config.json`` chooses the model."""
         arch, model_config = load_config(model_dir)
         spec = arch.build_spec(model_config)
+        config = cls._servable(spec, config, verbose)
         expected = {name: request.shape for name, request in expected_tensors(spec).items()}
         tensors = load_checkpoint(model_dir, expected, spec.ignorable)
         engine = cls(spec, tensors, config, verbose=verbose)
@@ -113,6 +127,7 @@ class Engine:
         """Random weights for ``model_config`` made in memory (no folder)."""
         from ..weights.random_init import random_tensors
         spec = resolve_architecture(model_config.architecture).build_spec(model_config)
+        config = cls._servable(spec, config, verbose)
         tensors = random_tensors(expected_tensors(spec), seed, dtype=stored_dtype or config.dtype)
         engine = cls(spec, tensors, config, verbose=verbose)
         engine.model_config = model_config

@@ -193,6 +193,24 @@ def test_generation_in_bfloat16_repeats_itself(folders):
     assert outputs[0] == outputs[1]
 
 
+def test_a_width_that_is_no_multiple_of_eight_is_served_in_float32(tmp_path):
+    """The bfloat16 kernels read rows of 16 bytes; such a model runs on the float32 kernels whatever is asked for."""
+    from stratakv_b200 import StepEntry
+    from zepavik_models import config, layer
+    raw = config(61, 100, [layer(5, 1, 12, 20, 9, 30), layer(2, 2, 10, 10, 0, 0)], buckets=11, mul_prev=2, mul_cur=3)
+    folder = make_folder(tmp_path / "odd", raw, seed=3, dtype=torch.bfloat16)
+    engine = engine_for(folder, "bfloat16")
+    assert engine.config.dtype == torch.float32
+    tokens = random_tokens(61, 90, seed=4)
+    weights = plain_zepavik.load_folder(folder)
+    ref = plain_zepavik.logits_of(*weights, tokens).numpy()
+    slot = engine.open_sequence()
+    got = engine.step([StepEntry(slot, tokens[:70], list(range(70)))])
+    check(got, ref[:70], "float32", "prompt")
+    for p in range(70, 90):
+        check(engine.step([StepEntry(slot, [tokens[p]], [0])]), ref[p:p + 1], "float32", f"position {p}")
+
+
 def test_positions_end_with_their_table(folders):
     from stratakv_b200 import StepEntry
     from stratakv_b200.engine.engine import StepError
