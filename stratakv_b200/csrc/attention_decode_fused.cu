@@ -130,6 +130,9 @@ __device__ __forceinline__ float4 f_add4(float4 a, const float* bias) {
     return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
 }
 
+// EXTRAS false: the instantiation without any of the optional steps (nothing of them is compiled in, so the plain
+// rotary decoder runs the code it ran before they existed).
+template <bool EXTRAS>
 __global__ void __launch_bounds__(FTHREADS, FHD <= 64 ? 2 : 1)
 decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __restrict__ cos_sin,
                               __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
@@ -166,7 +169,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     const int my_end = min(end_group, my_first + per_split);
     const int n_chunks = my_end > my_first ? (my_end - my_first + FWARPS - 1) / FWARPS : 0;
     const float scale_log2 = scale * 1.4426950408889634f;
-    const float* token = qkv + (size_t)seq * finish.row_stride;
+    const float* token = qkv + (size_t)seq * (EXTRAS ? finish.row_stride : q_dim + 2 * kv_dim);
     const int newest_group = pos >> 4;
     const bool owns_newest = newest_group >= my_first && newest_group < my_end;
 
@@ -226,10 +229,12 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
         for (int i = threadIdx.x; i < items; i += FTHREADS) {
             const int item = i / (HALF / 4), quad = i - item * (HALF / 4);
             const float* x = item < rows ? token + (size_t)(head0 + item) * FHD : token + q_dim + (size_t)kv_head * FHD;
-            const float* x_bias = item < rows ? (finish.q_bias ? finish.q_bias + (size_t)(head0 + item) * FHD : nullptr)
-                                              : (finish.k_bias ? finish.k_bias + (size_t)kv_head * FHD : nullptr);
             float4 a = *(const float4*)(x + 4 * quad), b = *(const float4*)(x + HALF + 4 * quad);
-            if (x_bias) { a = f_add4(a, x_bias + 4 * quad); b = f_add4(b, x_bias + HALF + 4 * quad); }
+            if (EXTRAS) {
+                const float* x_bias = item < rows ? (finish.q_bias ? finish.q_bias + (size_t)(head0 + item) * FHD : nullptr)
+                                                  : (finish.k_bias ? finish.k_bias + (size_t)kv_head * FHD : nullptr);
+                if (x_bias) { a = f_add4(a, x_bias + 4 * quad); b = f_add4(b, x_bias + HALF + 4 * quad); }
+            }
             const float xa[4] = {a.x, a.y, a.z, a.w}, xb[4] = {b.x, b.y, b.z, b.w};
             float first[4], second[4];
 #pragma unroll
@@ -248,7 +253,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                 *(uint2*)(k_cache + new_at + HALF + 4 * quad) = high;
             }
         }
-        if (owns_newest && write_kv && finish.value_norm) {
+        if (EXTRAS && owns_newest && write_kv && finish.value_norm) {
             // the new value row divided by its root mean square: the first warp holds the row (the launcher
             // admits head sizes up to 128 here), four numbers a lane
             if (warp == 0) {
@@ -273,7 +278,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                 uint2 packed;
                 if (write_kv) {
                     float4 v = *(const float4*)(token + q_dim + kv_dim + (size_t)kv_head * FHD + 4 * quad);
-                    if (finish.v_bias) v = f_add4(v, finish.v_bias + (size_t)kv_head * FHD + 4 * quad);
+                    if (EXTRAS && finish.v_bias) v = f_add4(v, finish.v_bias + (size_t)kv_head * FHD + 4 * quad);
                     packed = make_uint2(f_pack(v.x, v.y), f_pack(v.z, v.w));
                     *(uint2*)(v_cache + new_at + 4 * quad) = packed;
                 } else {
@@ -335,7 +340,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                 for (int e = 0; e < 4; ++e) {
                     const int key = j0 + 8 * t + 2 * tig + (e & 1);
                     float v = (key < ctx && key >= lo) ? s[t][e] * scale_log2 : -INFINITY;
-                    if (extras.bias && key < ctx && key >= lo && g + 8 * (e >> 1) < rows)
+                    if (EXTRAS && extras.bias && key < ctx && key >= lo && g + 8 * (e >> 1) < rows)
                         v -= __ldg(extras.bias + (size_t)(head0 + g + 8 * (e >> 1)) * extras.bias_len + min(pos - key, extras.bias_len - 1));
                     s[t][e] = v;
                     tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
@@ -447,7 +452,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
             total += weight * slots[b * FPITCH + d];
             sum += weight * slots[b * FPITCH + FHD + 1];
         }
-        out[((size_t)seq * num_heads + head0 + r) * FHD + d] = __float2bfloat16_rn(total / sum * gate_factor(extras, seq, head0 + r));
+        out[((size_t)seq * num_heads + head0 + r) * FHD + d] = __float2bfloat16_rn(EXTRAS ? total / sum * gate_factor(extras, seq, head0 + r) : total / sum);
     }
 }
 
@@ -499,9 +504,10 @@ SKV_EXPORT int skv_attention_decode_fused_extras(const float* qkv, int row_strid
         if (cudaGetDevice(&device) != cudaSuccess ||
             cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
             return fail("skv_attention_decode_fused", "cannot read the number of SMs");
-        const cudaError_t status = cudaFuncSetAttribute(decode_attention_fused_kernel,
-                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM_LIMIT);
-        if (status != cudaSuccess) return fail("skv_attention_decode_fused", cudaGetErrorString(status));
+        for (auto kernel : {decode_attention_fused_kernel<false>, decode_attention_fused_kernel<true>}) {
+            const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM_LIMIT);
+            if (status != cudaSuccess) return fail("skv_attention_decode_fused", cudaGetErrorString(status));
+        }
         sm_count = count;
     }
     // Two stages of 128 keys let two blocks share an SM.  A block that has an SM to itself, and whose piece of
@@ -529,8 +535,9 @@ SKV_EXPORT int skv_attention_decode_fused_extras(const float* qkv, int row_strid
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = pdl_enabled() ? 2 : 1;
+    const bool any_extras = q_bias || k_bias || v_bias || value_norm || bias || gate || row_stride != row_floats;
     const cudaError_t status = cudaLaunchKernelEx(
-        &config, decode_attention_fused_kernel, qkv, (const float2*)cos_sin, (__nv_bfloat16*)k_cache,
+        &config, any_extras ? decode_attention_fused_kernel<true> : decode_attention_fused_kernel<false>, qkv, (const float2*)cos_sin, (__nv_bfloat16*)k_cache,
         (__nv_bfloat16*)v_cache, block_table, table_width, ctx_after, (__nv_bfloat16*)out, num_heads, num_kv_heads,
         block_size, scale, window, splits, m_tiles, write_kv, block_shift, stages, finish, extras);
     if (status != cudaSuccess) return fail("skv_attention_decode_fused", cudaGetErrorString(status));

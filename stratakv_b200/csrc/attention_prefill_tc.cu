@@ -141,6 +141,8 @@ enum { B_Q = 0, B_KF = 1, B_VF = B_KF + K_STAGES, B_SF = B_VF + V_STAGES, B_SE =
 // memory) needs no rescaling and probabilities stay below 2^RESCALE_MARGIN.
 constexpr float RESCALE_MARGIN = 8.0f;
 
+// EXTRAS false: the instantiation without the bias table and the gate (nothing of them is compiled in).
+template <bool EXTRAS>
 __global__ void __launch_bounds__(ATHREADS, AHD <= 64 ? 2 : 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
@@ -309,8 +311,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const float scale_log2 = scale * 1.4426950408889634f;
         // with a bias by distance the scores are brought to units of log2 when the bias is taken off them,
         // and what follows multiplies by one
-        const float* bias_row = extras.bias ? extras.bias + (size_t)head * extras.bias_len : nullptr;
-        const float unit = bias_row ? 1.0f : scale_log2;
+        const float* bias_row = EXTRAS && extras.bias ? extras.bias + (size_t)head * extras.bias_len : nullptr;
+        const float unit = EXTRAS && bias_row ? 1.0f : scale_log2;
         float used_max = -INFINITY, row_sum = 0.0f;                   // in units of log2, after the scale
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
@@ -341,7 +343,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     sc[32 + e] = visible(key0 + 32 + e) ? __uint_as_float(v1[e]) : -INFINITY;
                 }
             }
-            if (bias_row) {
+            if (EXTRAS && bias_row) {
                 const int nearest = pos - key0 - (ABN - 1);            // the distance of the tile's last key
                 if (nearest >= 0 && pos - key0 < extras.bias_len) {
                     // every distance of the tile lies inside the table: one load and one multiply-add a score
@@ -417,7 +419,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok && n_tiles > 0) ok = a_wait(bar(B_PE, (n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, flag);
         if (ok && n_tiles > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inverse = gate_factor(extras, q_begin + min(q_row, q_len - 1), head) / row_sum;
+            const float inverse = (EXTRAS ? gate_factor(extras, q_begin + min(q_row, q_len - 1), head) : 1.0f) / row_sum;
             __nv_bfloat16* dst = out + ((size_t)(q_begin + min(q_row, q_len - 1)) * num_heads + head) * AHD;
 #pragma unroll 1
             for (int c = 0; c < AHD; c += 32) {
@@ -529,12 +531,14 @@ SKV_EXPORT int skv_attention_prefill_tc_extras(const void* q, const void* k_cach
     const size_t smem = (size_t)(ACH + 2) * TILE_BYTES + (size_t)(K_STAGES + V_STAGES) * ACH * KV_TILE_BYTES + B_COUNT * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
-        const cudaError_t status = cudaFuncSetAttribute(prefill_attention_tc_kernel,
-                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (status != cudaSuccess) return fail("skv_attention_prefill_tc", cudaGetErrorString(status));
+        for (auto kernel : {prefill_attention_tc_kernel<false>, prefill_attention_tc_kernel<true>}) {
+            const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (status != cudaSuccess) return fail("skv_attention_prefill_tc", cudaGetErrorString(status));
+        }
         configured = true;
     }
-    return launch_pdl("skv_attention_prefill_tc", prefill_attention_tc_kernel, dim3(num_heads, (unsigned)blocks),
+    return launch_pdl("skv_attention_prefill_tc", bias || gate ? prefill_attention_tc_kernel<true> : prefill_attention_tc_kernel<false>,
+                      dim3(num_heads, (unsigned)blocks),
                       dim3(ATHREADS), smem, stream, map_q, map_k, map_v, block_table, table_width, cu_q, ctx_after,
                       (__nv_bfloat16*)out, num_heads, num_kv_heads, block_size, rows_per_load, scale, window,
                       tiles_per_seq, flag, extras);

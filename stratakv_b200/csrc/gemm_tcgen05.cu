@@ -165,7 +165,6 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) 
 // 256-column tile took longer than the tile's main loop (2,048 x 11,264 x 2,048: 76.7 us against 63.8 us).  Past
 // z = -88 the exponential overflows to infinity and the quotient is -0, the right limit.
 __device__ __forceinline__ float gate_activation(float g, int act) {
-    if (act == ACT_RELU2) return relu_squared(g);
     const float z = act == ACT_GELU_TANH ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
     return __fdividef(g, 1.0f + __expf(-z));
 }
@@ -174,7 +173,8 @@ __device__ __forceinline__ float gate_activation(float g, int act) {
 // the test sits outside the unrolled loop, so a store without an activation pays one branch per 32 values and one
 // with the square of relu two instructions a value.  silu and the tanh form of gelu are gate_activation's.
 __device__ __forceinline__ float store_activation(float x, int act) {
-    return (act & ACT_ON_STORE) ? gate_activation(x, act & 0xff) : x;
+    if (!(act & ACT_ON_STORE)) return x;
+    return (act & 0xff) == ACT_RELU2 ? relu_squared(x) : gate_activation(x, act & 0xff);
 }
 
 __device__ __forceinline__ void activate_for_store(uint32_t (&v)[32], int act) {
@@ -994,10 +994,14 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
                             __float2bfloat16_rn(gate_activation(__uint_as_float(v[j]), act) * up);
                 }
             } else if (n < N) {
-                if (mode == TC_MODE_STORE) {
+                if (mode == TC_MODE_STORE && (act & ACT_ON_STORE)) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (c + j < M) ((__nv_bfloat16*)out)[(size_t)(c + j) * N + n] = __float2bfloat16_rn(store_activation(__uint_as_float(v[j]), act));
+                } else if (mode == TC_MODE_STORE) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c + j < M) ((__nv_bfloat16*)out)[(size_t)(c + j) * N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
                 } else if (mode == TC_MODE_STORE_F32) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
@@ -1332,6 +1336,8 @@ int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K,
     if (K % 8 != 0) return fail("skv_linear(tcgen05)", "the inner size must be a multiple of 8 (16-byte rows)");
     if (((uintptr_t)a | (uintptr_t)w) & 15) return fail("skv_linear(tcgen05)", "operands must be 16-byte aligned");
     if (mode == TC_MODE_GATED && N % 16 != 0) return fail("skv_linear(tcgen05)", "a gated weight needs a multiple of 16 rows");
+    if (mode == TC_MODE_GATED && act == ACT_RELU2)
+        return fail("skv_linear(tcgen05)", "the square of relu is an activation of stores, not of a gate, on these kernels");
     // More tiles of 128 weight rows than SMs: rings half as deep, so that two blocks share an SM and one's set-up and
     // epilogue run under the other's stream (64 tokens, 22,016 x 4,096: 54.0 -> 39.3 us; 28,672 x 4,096: 56.0 -> 46.0;
     // 32,000 x 2,048: 26.3 -> 23.4).  With fewer tiles the deep ring of a block alone on its SM is faster (2,048 x
