@@ -182,6 +182,27 @@ def test_greedy_generation_through_the_engine(folders, name):
     assert engine.cache.all_free()
 
 
+def test_command_line_generates_from_a_zepavik_folder(folders):
+    """bin/stratakv_cli opens the folder through the registry like every other entry point; greedy, float32."""
+    import subprocess
+    import sys
+    from helpers import ROOT
+    name = "ZB"
+    folder = folders[name, "float32"]
+    prompt = random_tokens(ZEPAVIK[name]["vocab"], 12, seed=8)
+    done = subprocess.run([sys.executable, str(ROOT / "bin" / "stratakv_cli"), "--dtype", "float32", "--temp", "0",
+                           "--ignore-eos", str(folder), "10", *[str(t) for t in prompt]],
+                          capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    sequence = [int(word) for word in done.stdout.split()]
+    assert len(sequence) == 22 and sequence[:12] == prompt
+    config, weights = plain_zepavik.load_folder(folder)
+    logits = plain_zepavik.logits_of(config, weights, sequence).numpy()
+    for at in range(12, 22):
+        row = logits[at - 1]
+        assert row[sequence[at]] >= row.max() - 1e-4 * max(1.0, abs(row.max()))
+
+
 def test_generation_in_bfloat16_repeats_itself(folders):
     """Generation through graphs and through eager steps chooses the same tokens (sequence state included)."""
     name, dtype = "ZA", "bfloat16"
