@@ -10,8 +10,15 @@
 //                      by chunks of 32 keys, everything after the loads in float.
 //
 // score(i, j) = (q_i . k_j) * scale - r1[head] * ln(1 + r2[head] * (i - j))      (r1 null: no such term)
+//               then cap * tanh(score / cap)                                      (cap 0: no cap)
 // visible:      0 <= i - j < window   (window 0: every earlier key)
-// out(i)      = softmax(score) . v  *  sigmoid(gate[i, head])                    (gate null: no gate)
+// out(i)      = softmax(score) . v  *  sigmoid(gate[i, head])                    (gate null: no gate; with
+//               gate_per_element the logit of every output number: gate[i, head * vdim + d])
+//
+// qkv_finish can also divide every query and key head by its root mean square (unit norm, no weight, or with a
+// weight on the keys, which is how a compressed latent per position is normed before it is cached), and multiply
+// the queries of position p by 1 + coef * ln(floor((p + 1) / every) + 1).  A row may hold queries only (keys and
+// values of another layer are used) or no values (vdim 0: the cached latent serves as key and value).
 //
 // Cache layout per entry: keys [block][kv_head][block_size][dim], values [block][kv_head][block_size][vdim].
 // These kernels are the same in every build of the library (no compile-time head size); they serve the
@@ -21,10 +28,20 @@
 namespace skv {
 
 constexpr int GEN_WARPS = 4;
-constexpr int GEN_MAX_VDIM = 256;                 // a lane keeps vdim / 32 accumulators
-constexpr int GEN_ACC = GEN_MAX_VDIM / 32;
+constexpr int GEN_MAX_VDIM = 512;                 // a lane keeps vdim / 32 accumulators: 8 up to 256, else 16
 
 constexpr int FINISH_WARPS = 8;
+
+// Optional steps of qkv_finish, all off when zero: the unit norm of query heads and of key heads (eps qk_eps; the
+// keys' with a weight [kv_heads * dim] if k_weight is given) and the queries' temperature by position.
+struct FinishExtras {
+    int key_dim;               // width of a key head where it differs from a query head's (a cached latent); else dim
+    int q_norm, k_norm;
+    float qk_eps;
+    const float* k_weight;
+    float q_temp_coef;
+    int q_temp_every;
+};
 
 template <typename T>
 __device__ __forceinline__ void finish_store4(T* out, float4 v, float factor) {
@@ -57,24 +74,31 @@ qkv_finish_kernel(const float* __restrict__ qkv, int row_stride, const float* __
                   const int* __restrict__ positions, const int* __restrict__ token_seq,
                   const int* __restrict__ block_table, int table_width, T* __restrict__ q_out,
                   T* __restrict__ k_cache, T* __restrict__ v_cache, int n_tokens, int num_heads, int num_kv_heads,
-                  int dim, int vdim, int block_size, int value_norm, float value_eps, int write_kv) {
+                  int dim, int vdim, int block_size, int value_norm, float value_eps, int write_kv,
+                  const FinishExtras extras) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
-    const int per_token = num_heads + 2 * num_kv_heads;
+    const int per_token = num_heads + (vdim > 0 ? 2 : 1) * num_kv_heads;
     const long long item = (long long)blockIdx.x * FINISH_WARPS + (threadIdx.x >> 5);
     if (item >= (long long)n_tokens * per_token) return;        // whole warps leave together
     const int t = (int)(item / per_token), which = (int)(item - (long long)t * per_token);
     const bool is_query = which < num_heads, is_key = !is_query && which < num_heads + num_kv_heads;
     if (!is_query && !write_kv) return;
     const int g = is_query ? which : (is_key ? which - num_heads : which - num_heads - num_kv_heads);
-    const int n = is_query || is_key ? dim : vdim;
+    const int kdim = extras.key_dim;
+    const int n = is_query ? dim : (is_key ? kdim : vdim);
     const float* x = qkv + (size_t)t * row_stride + (is_query ? (size_t)g * dim
-                     : is_key ? (size_t)num_heads * dim + (size_t)g * dim
-                              : (size_t)(num_heads + num_kv_heads) * dim + (size_t)g * vdim);
+                     : is_key ? (size_t)num_heads * dim + (size_t)g * kdim
+                              : (size_t)num_heads * dim + (size_t)num_kv_heads * kdim + (size_t)g * vdim);
     const float* bias_base = is_query ? q_bias : (is_key ? k_bias : v_bias);
     const float* bias = bias_base ? bias_base + (size_t)g * n : nullptr;
-    const bool normed = !is_query && !is_key && value_norm;
+    const bool normed = (!is_query && !is_key && value_norm) || (is_query && extras.q_norm) || (is_key && extras.k_norm);
+    const float norm_eps = is_query || is_key ? extras.qk_eps : value_eps;
+    const float* weight = is_key && extras.k_weight ? extras.k_weight + (size_t)g * n : nullptr;
+    float temperature = 1.0f;
+    if (is_query && extras.q_temp_every > 0)
+        temperature = 1.0f + extras.q_temp_coef * logf((float)((positions[t] + 1) / extras.q_temp_every) + 1.0f);
 
     float4 held[2];
     if (VEC) {
@@ -100,12 +124,19 @@ qkv_finish_kernel(const float* __restrict__ qkv, int row_stride, const float* __
 #pragma unroll
             for (int u = 0; u < 2; ++u)
                 squares += held[u].x * held[u].x + held[u].y * held[u].y + held[u].z * held[u].z + held[u].w * held[u].w;
-            factor = 1.0f / sqrtf(warp_sum(squares) / (float)n + value_eps);
+            factor = 1.0f / sqrtf(warp_sum(squares) / (float)n + norm_eps);
         }
+        factor *= temperature;
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             const int i = 4 * lane + 128 * u;
-            if (i < n) finish_store4<T>(out + i, held[u], factor);
+            if (i < n) {
+                if (weight) {
+                    const float4 w4 = *(const float4*)(weight + i);
+                    held[u].x *= w4.x; held[u].y *= w4.y; held[u].z *= w4.z; held[u].w *= w4.w;
+                }
+                finish_store4<T>(out + i, held[u], factor);
+            }
         }
         return;
     }
@@ -115,9 +146,11 @@ qkv_finish_kernel(const float* __restrict__ qkv, int row_stride, const float* __
             const float v = x[d] + (bias ? bias[d] : 0.0f);
             squares = fmaf(v, v, squares);
         }
-        factor = 1.0f / sqrtf(warp_sum(squares) / (float)n + value_eps);
+        factor = 1.0f / sqrtf(warp_sum(squares) / (float)n + norm_eps);
     }
-    for (int d = lane; d < n; d += 32) out[d] = from_float<T>((x[d] + (bias ? bias[d] : 0.0f)) * factor);
+    factor *= temperature;
+    for (int d = lane; d < n; d += 32)
+        out[d] = from_float<T>((x[d] + (bias ? bias[d] : 0.0f)) * factor * (weight ? weight[d] : 1.0f));
 }
 
 __device__ __forceinline__ float general_dot(const float* __restrict__ q, const float* __restrict__ row, int dim) {
@@ -153,14 +186,14 @@ __device__ __forceinline__ float general_dot(const float* __restrict__ q, const 
     return sum;
 }
 
-template <typename T>
+template <typename T, int GEN_ACC>
 __global__ void __launch_bounds__(GEN_WARPS * 32)
 attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                          const int* __restrict__ block_table, int table_width, const int* __restrict__ positions,
                          const int* __restrict__ token_seq, T* __restrict__ out, int n_tokens, int num_heads,
                          int num_kv_heads, int dim, int vdim, int block_size, float scale, int window,
                          const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ gate,
-                         int gate_stride, int out_stride) {
+                         int gate_stride, int out_stride, float softcap, int gate_per_element) {
     extern __shared__ __align__(16) float general_q[];          // [GEN_WARPS][dim rounded up to 4]
     pdl_launch_dependents();
     pdl_wait();
@@ -194,6 +227,7 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
             row = ((size_t)block * num_kv_heads + kv_head) * block_size + (j % block_size);
             score = general_dot(qs, k_cache + row * dim, dim) * scale;
             if (r1) score -= slope * log1pf(reach * (float)(pos - j));
+            if (softcap > 0.0f) score = softcap * tanhf(score / softcap);
         }
         const float new_max = fmaxf(running_max, warp_max(score));
         const float p = valid ? expf(score - new_max) : 0.0f;
@@ -215,12 +249,17 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
         }
     }
     float factor = 1.0f / running_sum;
-    if (gate) factor *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + head]));
+    if (gate && !gate_per_element) factor *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + head]));
+    const float* gate_row = gate && gate_per_element ? gate + (size_t)t * gate_stride + (size_t)head * vdim : nullptr;
     T* out_row = out + (size_t)t * out_stride + (size_t)head * vdim;
 #pragma unroll
     for (int i = 0; i < GEN_ACC; ++i) {
         const int d = lane + 32 * i;
-        if (d < vdim) out_row[d] = from_float<T>(acc[i] * factor);
+        if (d < vdim) {
+            float value = acc[i] * factor;
+            if (gate_row) value *= 1.0f / (1.0f + expf(-gate_row[d]));
+            out_row[d] = from_float<T>(value);
+        }
     }
     // columns that pad a row for the projection after it are zero
     if (head == num_heads - 1)
@@ -237,23 +276,29 @@ SKV_EXPORT int skv_qkv_finish(const float* qkv, int row_stride, const float* q_b
                               const float* v_bias, const int* positions, const int* token_seq,
                               const int* block_table, int table_width, void* q_out, void* k_cache, void* v_cache,
                               int n_tokens, int num_heads, int num_kv_heads, int dim, int vdim, int block_size,
-                              int value_norm, float value_eps, int write_kv, cudaStream_t stream) {
+                              int value_norm, float value_eps, int write_kv, int q_norm, int k_norm, float qk_eps,
+                              const float* k_weight, float q_temp_coef, int q_temp_every, int key_dim,
+                              cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (num_heads <= 0 || num_kv_heads <= 0 || dim <= 0 || vdim <= 0 || block_size <= 0)
+    if (num_heads <= 0 || num_kv_heads <= 0 || dim <= 0 || vdim < 0 || block_size <= 0)
         return fail("skv_qkv_finish", "head counts, head sizes and block_size must be positive");
-    if (row_stride < (num_heads + num_kv_heads) * dim + num_kv_heads * vdim)
+    if (key_dim <= 0) key_dim = dim;
+    if (row_stride < (write_kv ? num_heads * dim + num_kv_heads * (key_dim + vdim) : num_heads * dim))
         return fail("skv_qkv_finish", "a row is shorter than its queries, keys and values");
-    const long long items = (long long)n_tokens * (num_heads + 2 * num_kv_heads);
+    if (q_temp_every < 0) return fail("skv_qkv_finish", "the temperature's period must not be negative");
+    const FinishExtras extras = {key_dim, q_norm, k_norm, qk_eps, k_weight, q_temp_coef, q_temp_every};
+    const long long items = (long long)n_tokens * (num_heads + (vdim > 0 ? 2 : 1) * num_kv_heads);
     const long long blocks = (items + FINISH_WARPS - 1) / FINISH_WARPS;
     if (blocks > 0x7fffffffLL) return fail("skv_qkv_finish", "too many tokens in one step");
-    const bool vec = dim % 4 == 0 && vdim % 4 == 0 && dim <= 256 && vdim <= 256 && row_stride % 4 == 0 &&
+    const bool vec = dim % 4 == 0 && vdim % 4 == 0 && key_dim % 4 == 0 && dim <= 256 && vdim <= 256 && key_dim <= 256 &&
+                     row_stride % 4 == 0 &&
                      (((uintptr_t)qkv | (uintptr_t)q_bias | (uintptr_t)k_bias | (uintptr_t)v_bias | (uintptr_t)q_out |
-                       (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;
+                       (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)k_weight) & 15) == 0;
     auto kernel = vec ? qkv_finish_kernel<skv_t, true> : qkv_finish_kernel<skv_t, false>;
     return launch_pdl("skv_qkv_finish", kernel, dim3((unsigned)blocks), dim3(FINISH_WARPS * 32), 0, stream, qkv,
                       row_stride, q_bias, k_bias, v_bias, positions, token_seq, block_table, table_width,
                       (skv_t*)q_out, (skv_t*)k_cache, (skv_t*)v_cache, n_tokens, num_heads, num_kv_heads, dim, vdim,
-                      block_size, value_norm, value_eps, write_kv);
+                      block_size, value_norm, value_eps, write_kv, extras);
 }
 
 // `r1`, `r2`: float [num_heads] or both null.  `gate`: float, the gate's logit of (token t, head h) at
@@ -263,11 +308,13 @@ SKV_EXPORT int skv_attention_general(const void* q, const void* k_cache, const v
                                      int table_width, const int* positions, const int* token_seq, void* out,
                                      int n_tokens, int num_heads, int num_kv_heads, int dim, int vdim, int block_size,
                                      float scale, int window, const float* r1, const float* r2, const float* gate,
-                                     int gate_stride, int out_stride, cudaStream_t stream) {
+                                     int gate_stride, int out_stride, float softcap, int gate_per_element,
+                                     cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_general", "heads must be a positive multiple of kv heads");
-    if (dim <= 0 || vdim <= 0 || vdim > GEN_MAX_VDIM) return fail("skv_attention_general", "value heads of 1 to 256 numbers are served");
+    if (dim <= 0 || vdim <= 0 || vdim > GEN_MAX_VDIM) return fail("skv_attention_general", "value heads of 1 to 512 numbers are served");
+    if (softcap < 0.0f) return fail("skv_attention_general", "the cap on the scores must not be negative");
     if (block_size <= 0 || window < 0) return fail("skv_attention_general", "bad block size or window");
     if (out_stride < num_heads * vdim) return fail("skv_attention_general", "a row of the output is shorter than its heads");
     if ((r1 == nullptr) != (r2 == nullptr)) return fail("skv_attention_general", "the distance bias needs both of its numbers per head");
@@ -276,8 +323,10 @@ SKV_EXPORT int skv_attention_general(const void* q, const void* k_cache, const v
     const long long items = (long long)n_tokens * num_heads;
     const long long blocks = (items + GEN_WARPS - 1) / GEN_WARPS;
     if (blocks > 0x7fffffffLL) return fail("skv_attention_general", "too many tokens in one step");
-    return launch_pdl("skv_attention_general", attention_general_kernel<skv_t>, dim3((unsigned)blocks),
+    auto kernel = vdim <= 256 ? attention_general_kernel<skv_t, 8> : attention_general_kernel<skv_t, 16>;
+    return launch_pdl("skv_attention_general", kernel, dim3((unsigned)blocks),
                       dim3(GEN_WARPS * 32), smem, stream, (const skv_t*)q, (const skv_t*)k_cache,
                       (const skv_t*)v_cache, block_table, table_width, positions, token_seq, (skv_t*)out, n_tokens,
-                      num_heads, num_kv_heads, dim, vdim, block_size, scale, window, r1, r2, gate, gate_stride, out_stride);
+                      num_heads, num_kv_heads, dim, vdim, block_size, scale, window, r1, r2, gate, gate_stride, out_stride,
+                      softcap, gate_per_element);
 }

@@ -98,7 +98,12 @@ inline int sm_count() {
 }
 
 // Activations of a gated feed-forward's gate, chosen by the part's spec (ops.ACTIVATIONS has the names).
-enum { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_RELU2 = 2, ACT_COUNT = 3 };
+enum { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_RELU2 = 2, ACT_SWIGLU_CLAMP = 3, ACT_COUNT = 4 };
+// How an activation travels through the projection kernels: its code in the low 8 bits, ACT_ON_STORE above them, and
+// in the high 32 bits the bits of one float that the activation may need (zero for those without a parameter, so a
+// plain code compares equal to its enum).
+typedef long long act_t;
+__device__ __forceinline__ float act_param(act_t act) { return __int_as_float((int)(act >> 32)); }
 // Added to an activation's code where a projection without a gate applies it to what it stores
 // (out = act(a . w^T), the plain feed-forward): the store epilogues look for this bit.
 constexpr int ACT_ON_STORE = 0x100;
@@ -108,6 +113,15 @@ __device__ __forceinline__ float gelu_tanh(float g) {
     return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
 }
 
+// A gated unit with both branches clamped (ACT_SWIGLU_CLAMP, parameter `limit`): g' = min(g, limit),
+// u' = clamp(u, -limit, limit), value g' * sigmoid(1.702 g') * (u' + 1).
+constexpr float SWIGLU_CLAMP_ALPHA = 1.702f;
+__device__ __forceinline__ float clamped_swiglu(float g, float u, float limit) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-SWIGLU_CLAMP_ALPHA * g)) * (u + 1.0f);
+}
+
 // relu(z)^2
 __device__ __forceinline__ float relu_squared(float z) {
     const float r = fmaxf(z, 0.0f);
@@ -115,9 +129,9 @@ __device__ __forceinline__ float relu_squared(float z) {
 }
 
 // What a store epilogue writes for the accumulated value v: v itself, or (ACT_ON_STORE) its activation.
-__device__ __forceinline__ float stored_value(float v, int act) {
+__device__ __forceinline__ float stored_value(float v, act_t act) {
     if (!(act & ACT_ON_STORE)) return v;
-    const int code = act & 0xff;
+    const int code = (int)(act & 0xff);
     if (code == ACT_RELU2) return relu_squared(v);
     if (code == ACT_GELU_TANH) return gelu_tanh(v);
     return v / (1.0f + expf(-v));                     // silu

@@ -164,22 +164,34 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) 
 // below the bfloat16 the product is rounded to.  With libm's expf and an IEEE division the gated epilogue of a
 // 256-column tile took longer than the tile's main loop (2,048 x 11,264 x 2,048: 76.7 us against 63.8 us).  Past
 // z = -88 the exponential overflows to infinity and the quotient is -0, the right limit.
-__device__ __forceinline__ float gate_activation(float g, int act) {
+__device__ __forceinline__ float gate_activation(float g, act_t act) {
     const float z = act == ACT_GELU_TANH ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
     return __fdividef(g, 1.0f + __expf(-z));
+}
+
+// What a gated projection stores for a gate value and its up value: act(gate) * up, or the clamped unit of
+// common.cuh (ACT_SWIGLU_CLAMP) with the same special-function exponential and quotient.
+__device__ __forceinline__ float gated_product(float g, float up, act_t act) {
+    if ((act & 0xff) == ACT_SWIGLU_CLAMP) {
+        const float limit = act_param(act);
+        g = fminf(g, limit);
+        up = fminf(fmaxf(up, -limit), limit);
+        return __fdividef(g, 1.0f + __expf(-SWIGLU_CLAMP_ALPHA * g)) * (up + 1.0f);
+    }
+    return gate_activation(g, act) * up;
 }
 
 // The activation of a projection that stores act(a . w^T) (ACT_ON_STORE in `act`), on 32 accumulator values at once:
 // the test sits outside the unrolled loop, so a store without an activation pays one branch per 32 values and one
 // with the square of relu two instructions a value.  silu and the tanh form of gelu are gate_activation's.
-__device__ __forceinline__ float store_activation(float x, int act) {
+__device__ __forceinline__ float store_activation(float x, act_t act) {
     if (!(act & ACT_ON_STORE)) return x;
-    return (act & 0xff) == ACT_RELU2 ? relu_squared(x) : gate_activation(x, act & 0xff);
+    return (act & 0xff) == ACT_RELU2 ? relu_squared(x) : gate_activation(x, (int)(act & 0xff));
 }
 
-__device__ __forceinline__ void activate_for_store(uint32_t (&v)[32], int act) {
+__device__ __forceinline__ void activate_for_store(uint32_t (&v)[32], act_t act) {
     if (!(act & ACT_ON_STORE)) return;
-    const int code = act & 0xff;
+    const int code = (int)(act & 0xff);
     if (code == ACT_RELU2) {
 #pragma unroll
         for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(relu_squared(__uint_as_float(v[e])));
@@ -215,7 +227,7 @@ __host__ __device__ inline int tile_band(int tile_rows, int K) {
 template <int BN>
 __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, int lane, uint8_t* slabs, int& buffer,
                                               const CUtensorMap* map_out, int tma_out, void* __restrict__ out, int M,
-                                              int N, int mode, int act, int m0, int n0) {
+                                              int N, int mode, act_t act, int m0, int n0) {
     const int m = m0 + quarter * 32 + lane;
     if (tma_out) {
         // Each thread builds 128 bytes of its output row in a swizzled slab of shared memory; one lane
@@ -246,10 +258,10 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, in
                         uint32_t packed[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            const float lo = gate_activation(__uint_as_float(v[16 * grp + 2 * j]), act) *
-                                             __uint_as_float(v[16 * grp + 8 + 2 * j]);
-                            const float hi = gate_activation(__uint_as_float(v[16 * grp + 2 * j + 1]), act) *
-                                             __uint_as_float(v[16 * grp + 8 + 2 * j + 1]);
+                            const float lo = gated_product(__uint_as_float(v[16 * grp + 2 * j]),
+                                                           __uint_as_float(v[16 * grp + 8 + 2 * j]), act);
+                            const float hi = gated_product(__uint_as_float(v[16 * grp + 2 * j + 1]),
+                                                           __uint_as_float(v[16 * grp + 8 + 2 * j + 1]), act);
                             const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
                             packed[j] = *(const uint32_t*)&pair;
                         }
@@ -305,10 +317,10 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, in
                         uint32_t packed[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            const float lo = gate_activation(__uint_as_float(v[16 * grp + 2 * j]), act) *
-                                             __uint_as_float(v[16 * grp + 8 + 2 * j]);
-                            const float hi = gate_activation(__uint_as_float(v[16 * grp + 2 * j + 1]), act) *
-                                             __uint_as_float(v[16 * grp + 8 + 2 * j + 1]);
+                            const float lo = gated_product(__uint_as_float(v[16 * grp + 2 * j]),
+                                                           __uint_as_float(v[16 * grp + 8 + 2 * j]), act);
+                            const float hi = gated_product(__uint_as_float(v[16 * grp + 2 * j + 1]),
+                                                           __uint_as_float(v[16 * grp + 8 + 2 * j + 1]), act);
                             const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
                             packed[j] = *(const uint32_t*)&pair;
                         }
@@ -472,7 +484,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, int tma_out, void* __restrict__ out, int M,
-                    int N, int K, int mode, int act, int* __restrict__ flag, const RopeArgs rope) {
+                    int N, int K, int mode, act_t act, int* __restrict__ flag, const RopeArgs rope) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
     // tensor memory is handed out in powers of two columns: two accumulators, each at the start of a half
     constexpr uint32_t TMEM_COLS = BN <= 64 ? 128 : (BN <= 128 ? 256 : 512), ACC_STRIDE = TMEM_COLS / 2;
@@ -664,7 +676,7 @@ template <int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const __grid_constant__ CUtensorMap map_out, int tma_out, void* __restrict__ out, int M,
-                         int N, int K, int mode, int act, int* __restrict__ flag, const RopeArgs rope) {
+                         int N, int K, int mode, act_t act, int* __restrict__ flag, const RopeArgs rope) {
     constexpr int BN = 256;                                  // the pair's tile: 256 rows (128 per block) x 256 columns
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = (BN / 2) * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
     constexpr uint32_t TMEM_COLS = 512, ACC_STRIDE = 256;
@@ -828,7 +840,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 template <int MP, int STAGES, int CH>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                               void* __restrict__ out, int M, int N, int K, int mode, int act, int splits,
+                               void* __restrict__ out, int M, int N, int K, int mode, act_t act, int splits,
                                int* __restrict__ flag) {
     constexpr uint32_t W_CHUNK = 128 * TC_BK * 2, X_CHUNK = MP * TC_BK * 2;
     constexpr uint32_t W_BYTES = W_CHUNK * CH, X_BYTES = X_CHUNK * CH, STAGE_BYTES = W_BYTES + X_BYTES;
@@ -991,7 +1003,7 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
                     const float up = __shfl_down_sync(0xffffffffu, __uint_as_float(v[j]), 8);
                     if ((lane & 8) == 0 && c + j < M && n < N)
                         ((__nv_bfloat16*)out)[(size_t)(c + j) * half_n + o] =
-                            __float2bfloat16_rn(gate_activation(__uint_as_float(v[j]), act) * up);
+                            __float2bfloat16_rn(gated_product(__uint_as_float(v[j]), up, act));
                 }
             } else if (n < N) {
                 if (mode == TC_MODE_STORE && (act & ACT_ON_STORE)) {
@@ -1127,7 +1139,7 @@ static int tensor_map_chunks(const void* base, int rows, int K, int box_rows, in
 static int tc_sm_count() { return sm_count(); }
 
 template <int BN, int STAGES>
-static int launch_tc(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
+static int launch_tc(const void* a, const void* w, void* out, int M, int N, int K, int mode, act_t act, int* flag,
                      cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
     CUtensorMap map_a, map_w, map_out;
     if (int code = tensor_map(a, M, K, 2, TC_BM, TC_BK, &map_a)) return code;
@@ -1208,7 +1220,7 @@ static int pair_slots() {
     return slots;
 }
 
-static int launch_pair(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
+static int launch_pair(const void* a, const void* w, void* out, int M, int N, int K, int mode, act_t act, int* flag,
                        cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
     CUtensorMap map_a, map_w, map_out;
     if (int code = tensor_map(a, M, K, 2, TC_BM, TC_BK, &map_a)) return code;
@@ -1251,7 +1263,7 @@ static double pair_cost(int M, int N, int K) {
 }
 
 template <int MP, int STAGES, int CH>
-static int launch_few_tokens(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+static int launch_few_tokens(const void* a, const void* w, void* out, int M, int N, int K, int mode, act_t act,
                              int* flag, cudaStream_t stream) {
     CUtensorMap map_w, map_x;
     if (CH == 1) {
@@ -1331,7 +1343,7 @@ static int choose_form(int M, int N, int K, int mode) {
     return wide <= narrow ? FORM_256 : FORM_128;
 }
 
-int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
+int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, act_t act, int* flag,
                    cudaStream_t stream) {
     if (K % 8 != 0) return fail("skv_linear(tcgen05)", "the inner size must be a multiple of 8 (16-byte rows)");
     if (((uintptr_t)a | (uintptr_t)w) & 15) return fail("skv_linear(tcgen05)", "operands must be 16-byte aligned");

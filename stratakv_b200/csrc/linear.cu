@@ -28,7 +28,7 @@ enum { MODE_STORE = 0, MODE_STORE_F32 = 1, MODE_ADD_F32 = 2, MODE_GATED = 3 };
 // with ACT_ON_STORE added to the activation's code.
 constexpr int MODE_STORE_ACT = 5;
 
-__device__ __forceinline__ float activate(float g, int act) {
+__device__ __forceinline__ float activate(float g, act_t act) {
     if (act == ACT_GELU_TANH) return gelu_tanh(g);
     if (act == ACT_RELU2) return relu_squared(g);
     // silu(g) = g * sigmoid(g); the two-branch sigmoid of the reference's CPU
@@ -37,8 +37,14 @@ __device__ __forceinline__ float activate(float g, int act) {
     return g * sig;
 }
 
+// What a gated projection stores for a gate value and its up value.
+__device__ __forceinline__ float gated_product(float gate, float up, act_t act) {
+    if ((act & 0xff) == ACT_SWIGLU_CLAMP) return clamped_swiglu(gate, up, act_param(act));
+    return activate(gate, act) * up;
+}
+
 template <typename T>
-__device__ __forceinline__ void epilogue_store(void* out, int mode, int M, int N, int m, int n, float v, int act) {
+__device__ __forceinline__ void epilogue_store(void* out, int mode, int M, int N, int m, int n, float v, act_t act) {
     if (m >= M || n >= N) return;
     const size_t at = (size_t)m * N + n;
     if (mode == MODE_STORE) ((T*)out)[at] = from_float<T>(stored_value(v, act));
@@ -55,7 +61,7 @@ constexpr int FBM = 64, FBN = 64, FBK = 16;
 
 __global__ void __launch_bounds__(256)
 linear_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, void* __restrict__ out,
-                  int M, int N, int K, int mode, int act) {
+                  int M, int N, int K, int mode, act_t act) {
     __shared__ float As[FBK][FBM + 4];
     __shared__ float Ws[FBK][FBN + 4];
     pdl_launch_dependents();
@@ -102,7 +108,7 @@ linear_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, void
                 if (n >= N) continue;
                 const int o = ((n >> 4) << 3) + (n & 7);
                 if (o < half_n)
-                    ((float*)out)[(size_t)m * half_n + o] = activate(acc[i][c], act) * acc[i][c + 2];
+                    ((float*)out)[(size_t)m * half_n + o] = gated_product(acc[i][c], acc[i][c + 2], act);
             }
         } else {
 #pragma unroll
@@ -115,7 +121,7 @@ struct NormArgs { const float* row_scale; const float* partials_in; int n_partia
                   const int* rows; float* partials; int partial_stride; unsigned int* counter;
                   const float* gamma_next; float eps_next; void* scaled_out; float* row_scale_out; };
 
-static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, act_t act,
                          int* flag, const NormArgs& norm, cudaStream_t stream) {
     (void)flag;
     if (norm.row_scale || norm.partials_in || norm.partials) return fail("skv_linear(float)", "the norm-fused form exists in the bfloat16 build only");
@@ -176,7 +182,7 @@ struct NormArgs {
 template <int TG, int U, bool STREAM, int MAX_WARPS>
 __global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS == 4 ? (TG == 1 ? 5 : (TG == 2 ? 5 : 2)) : (MAX_WARPS == 8 && TG <= 2 ? 2 : 1))
 skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
-                          void* __restrict__ out, int M, int N, int K, int mode, int act, const NormArgs norm) {
+                          void* __restrict__ out, int M, int N, int K, int mode, act_t act, const NormArgs norm) {
     extern __shared__ float red[];                 // [warps][16][8*TG + 1], [8*TG] factors, [8*TG][n_partials_in] partial sums
     constexpr int COLS = 8 * TG, PITCH = COLS + 1;
     pdl_launch_dependents();
@@ -294,7 +300,7 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
             const int o = (n0 >> 1) + r, gm = m0 + m;
             if (gm < M && o < half_n) {
                 const float gate = red[(size_t)r * PITCH + m], up = red[(size_t)(r + 8) * PITCH + m];
-                ((__nv_bfloat16*)out)[(size_t)gm * half_n + o] = __float2bfloat16_rn(activate(gate, act) * up);
+                ((__nv_bfloat16*)out)[(size_t)gm * half_n + o] = __float2bfloat16_rn(gated_product(gate, up, act));
             }
         }
     } else if (mode == MODE_ADD_F32 && norm.partials) {
@@ -340,7 +346,7 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
 }
 
 template <int TG, int U, int MAX_WARPS>
-static int launch_skinny_as(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+static int launch_skinny_as(const void* a, const void* w, void* out, int M, int N, int K, int mode, act_t act,
                             int warps, const NormArgs& norm, cudaStream_t stream) {
     const int row_tiles = (N + 15) / 16, chunks = (M + 8 * TG - 1) / (8 * TG);
     const size_t smem = ((size_t)warps * 16 * (8 * TG + 1) + 8 * TG + (size_t)8 * TG * (norm.partials_in ? (norm.n_partials_in + 3) & ~3 : 0)) * sizeof(float);
@@ -363,7 +369,7 @@ static int launch_skinny_as(const void* a, const void* w, void* out, int M, int 
 // each and the tiles are no more than the SMs (a block of 16 warps has an SM to itself; 256 tiles of 8 warps run as
 // one wave, of 16 warps as two).  Never more warps than k steps.
 template <int TG, int U, int MAX_WARPS>
-static int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+static int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int mode, act_t act,
                          const NormArgs& norm, cudaStream_t stream) {
     const int row_tiles = (N + 15) / 16, chunks = (M + 8 * TG - 1) / (8 * TG);
     const int steps = (K + 31) / 32;
@@ -381,10 +387,10 @@ static int launch_skinny(const void* a, const void* w, void* out, int M, int N, 
 }
 
 // gemm_tcgen05.cu: the tensor-memory GEMM that serves steps with many tokens
-int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
+int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, act_t act, int* flag,
                    cudaStream_t stream);
 
-static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, act_t act,
                          int* flag, const NormArgs& norm, cudaStream_t stream) {
     if (K % 8 != 0)
         return fail("skv_linear(bfloat16)", "the inner size must be a multiple of 8 (16-byte rows)");
@@ -408,12 +414,13 @@ static int launch_linear(const void* a, const void* w, void* out, int M, int N, 
 
 using namespace skv;
 
-static int check_linear(int M, int N, int K, int mode, int act) {
+static int check_linear(int M, int N, int K, int mode, act_t act) {
     if (N <= 0 || K <= 0) return fail("skv_linear", "N and K must be positive");
     if (mode < 0 || mode > 3) return fail("skv_linear", "unknown epilogue mode");
     if (mode == MODE_GATED && N % 16 != 0)
         return fail("skv_linear", "a gated weight must have a multiple of 16 rows (gate/up tiles of 8)");
-    if ((act & 0xff) >= ACT_COUNT || (act & ~(0xff | ACT_ON_STORE)) || ((act & ACT_ON_STORE) && mode != MODE_STORE))
+    if ((act & 0xff) >= ACT_COUNT || (act & 0xffffffffLL & ~(0xffLL | ACT_ON_STORE)) || ((act & ACT_ON_STORE) && mode != MODE_STORE) ||
+        ((act & 0xff) == ACT_SWIGLU_CLAMP && mode != MODE_GATED))
         return fail("skv_linear", "unknown activation");
     (void)M;
     return 0;
@@ -424,7 +431,7 @@ static int check_linear(int M, int N, int K, int mode, int act) {
 // projection after the next norm needs (see NormArgs): the scaled rows, and the rows' sums of squares as
 // `partials` [M, partial_stride] with partial_stride >= N/16 rounded up.  With `counter` (one zeroed word, left
 // zeroed) it finishes them into `row_scale_out` too.
-SKV_EXPORT int skv_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+SKV_EXPORT int skv_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, act_t act,
                           int* flag, void* scaled_out, const float* gamma_next, float* partials, int partial_stride,
                           float* row_scale_out, float eps_next, unsigned int* counter, cudaStream_t stream) {
     if (M <= 0) return 0;
@@ -451,7 +458,7 @@ SKV_EXPORT int skv_linear(const void* a, const void* w, void* out, int M, int N,
 // 1 / sqrt(sum of partials[row, :n_partials] / K + eps).  bfloat16 build, at most 64 tokens.
 SKV_EXPORT int skv_linear_normed(const void* a, const float* row_scale, const float* partials, int n_partials,
                                  int partial_stride, float eps, const int* rows, const void* w, void* out, int M,
-                                 int N, int K, int mode, int act, cudaStream_t stream) {
+                                 int N, int K, int mode, act_t act, cudaStream_t stream) {
     if (M <= 0) return 0;
     if (mode == MODE_STORE_ACT) { mode = MODE_STORE; act |= ACT_ON_STORE; }
     if (int code = check_linear(M, N, K, mode, act)) return code;

@@ -87,6 +87,9 @@ class Model:
             self.embedding.state_entry = spec.num_cache_entries()
         # Raised by kernels: bit 0 = token id outside the vocabulary, bit 3 = position beyond a table.
         self.flags = torch.zeros(1, dtype=torch.int32, device=runtime.device)
+        # A callable ``(run index, stream)`` that sees the float32 residual stream after every run of a layer (for
+        # tests and for finding the layer where two implementations part); None in service.
+        self.layer_probe = None
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.embedding.bind(tensors)
@@ -143,7 +146,11 @@ class Model:
         self.embedding.forward(step, x, self.flags, stats=stats)
         for index, entry in enumerate(spec.schedule):
             step.norm_after_layer = readers[index + 1]
+            following = spec.schedule[index + 1].layer if index + 1 < len(spec.schedule) else None
+            step.next_layer_norm = self.layers[following].mixer_norm if following is not None else None
             self.layers[entry.layer].forward(step, x, entry)
+            if self.layer_probe is not None:
+                self.layer_probe(index, x)
         if n_want == 0:
             return None
         if stats is not None and final is not None:

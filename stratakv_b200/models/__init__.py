@@ -1,3 +1,4 @@
 """Architectures.  Importing this package registers every one of them."""
 from . import llama  # noqa: F401
+from . import povusun  # noqa: F401
 from . import zepavik  # noqa: F401

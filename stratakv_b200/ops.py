@@ -7,6 +7,7 @@ raise; nothing falls back to the CPU or to library model code.
 from __future__ import annotations
 
 import ctypes
+import struct
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -18,7 +19,21 @@ MODE_STORE, MODE_STORE_F32, MODE_ADD_F32, MODE_GATED = 0, 1, 2, 3
 MODE_QKV_ROPE = 4          # (linear_qkv_rope's own epilogue; named for Kernels.linear_form)
 MODE_ACT = 5               # out = act(a . w^T) in the compute dtype: the first projection of a feed-forward without a gate
 # activations that every projection kernel implements, on a gate or on what it stores (csrc/common.cuh)
-ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1, "relu2": 2, "relu_squared": 2}
+ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1, "relu2": 2, "relu_squared": 2,
+               "swiglu_clamp": 3}
+# activations that take one number (``activation_param``): the clamp of both branches of "swiglu_clamp", a gated unit
+# min(g, c) * sigmoid(1.702 min(g, c)) * (clamp(u, -c, c) + 1); it is an activation of gated projections only
+PARAMETRIC_ACTIVATIONS = ("swiglu_clamp",)
+
+
+def activation_word(activation: str, param: float = 0.0):
+    """An activation as the kernels take it: its code in the low bits, the bits of its float parameter in the high 32."""
+    code = ACTIVATIONS[activation]
+    if activation in PARAMETRIC_ACTIVATIONS:
+        code |= struct.unpack("<I", struct.pack("<f", float(param)))[0] << 32
+    return ctypes.c_longlong(code)
+
+
 _DTYPE_NAMES = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
 
 
@@ -161,7 +176,8 @@ class Kernels:
         self._check(self.lib.skv_rmsnorm(_ptr(x), _ptr(gamma), ctypes.c_float(eps), _ptr(out), _ptr(rows),
                                          n_rows, hidden, _stream()), "rmsnorm")
 
-    def linear(self, a, w, out, mode: int = MODE_STORE, activation: str = "silu", flag=None, stats=None):
+    def linear(self, a, w, out, mode: int = MODE_STORE, activation: str = "silu", flag=None, stats=None,
+               activation_param: float = 0.0):
         """out = a[M,K] . w[N,K]^T with the epilogue ``mode``.
 
         ``a`` may be ``residual.NormedRows``: the norm is applied while the activations are
@@ -188,6 +204,8 @@ class Kernels:
             raise KernelError(f"linear: out must be [{M}, {out_cols}], got {list(out.shape)}")
         if activation not in ACTIVATIONS:
             raise KernelError(f"linear: unknown activation '{activation}'")
+        if activation in PARAMETRIC_ACTIVATIONS and mode == MODE_ACT:
+            raise KernelError(f"linear: '{activation}' is an activation of gated projections")
         if stats is not None and mode != MODE_ADD_F32:
             raise KernelError("linear: statistics are kept by the residual-add mode only")
         if normed is not None:
@@ -203,10 +221,11 @@ class Kernels:
                 factor = (_ptr(normed.row_scale), _NULL, 0, 0, ctypes.c_float(0.0))
             self._check(self.lib.skv_linear_normed(
                 _ptr(normed.scaled), *factor, _ptr(normed.rows), _ptr(w), _ptr(out), M, N, K, mode,
-                ACTIVATIONS[activation], _stream()), "linear")
+                activation_word(activation, activation_param), _stream()), "linear")
             return
         fold = self._fold_target(stats, M, N)
-        self._check(self.lib.skv_linear(_ptr(a), _ptr(w), _ptr(out), M, N, K, mode, ACTIVATIONS[activation],
+        self._check(self.lib.skv_linear(_ptr(a), _ptr(w), _ptr(out), M, N, K, mode,
+                                        activation_word(activation, activation_param),
                                         _ptr(flag if flag is not None else self.error_flag), *(fold or _NO_FOLD), _stream()),
                     "linear")
         if stats is not None:
@@ -436,15 +455,25 @@ class Kernels:
 
     def qkv_finish(self, qkv, q_out, k_cache, v_cache, positions, token_seq, block_table, num_heads: int,
                    num_kv_heads: int, dim: int, vdim: int, block_size: int, q_bias=None, k_bias=None, v_bias=None,
-                   value_norm_eps=None, write_kv: bool = True):
+                   value_norm_eps=None, write_kv: bool = True, q_norm: bool = False, k_norm: bool = False,
+                   qk_norm_eps: float = 0.0, k_norm_weight=None, q_temperature=None, key_dim: int = 0):
         """From float32 rows ``[q | k | v | ...]`` of a fused projection: biases added, each value head divided by
         its root mean square (``value_norm_eps`` not None), queries to ``q_out`` and keys and values to the cache
-        in the compute dtype.  Any head sizes; keys ``dim`` and values ``vdim`` wide."""
+        in the compute dtype.  Any head sizes; keys ``dim`` and values ``vdim`` wide.
+
+        ``q_norm`` / ``k_norm``: every query / key head divided by its root mean square (``qk_norm_eps``), the keys
+        then times ``k_norm_weight`` (float32 ``[kv_heads * dim]``) if given.  ``q_temperature`` ``(coef, every)``:
+        the queries at position p times ``1 + coef * ln(floor((p + 1) / every) + 1)``.  ``vdim`` 0 with ``v_cache``
+        None: the rows hold no values.  With ``write_kv`` false a row need hold its queries only.  ``key_dim``: the
+        width of a key head where it is not a query head's (a compressed latent that is cached as the one key)."""
+        key_dim = key_dim or dim
         self._want(qkv, torch.float32, "qkv"); self._want(q_out, self.dtype, "q_out")
         self._want(positions, torch.int32, "positions"); self._want(token_seq, torch.int32, "token_seq")
         self._want(block_table, torch.int32, "block_table")
-        self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
-        for name, bias, width in (("q_bias", q_bias, num_heads * dim), ("k_bias", k_bias, num_kv_heads * dim),
+        self._want(k_cache, self.dtype, "k_cache")
+        if v_cache is not None:
+            self._want(v_cache, self.dtype, "v_cache")
+        for name, bias, width in (("q_bias", q_bias, num_heads * dim), ("k_bias", k_bias, num_kv_heads * (key_dim or dim)),
                                   ("v_bias", v_bias, num_kv_heads * vdim)):
             if bias is not None:
                 self._want(bias, torch.float32, name)
@@ -453,19 +482,31 @@ class Kernels:
         n = qkv.shape[0]
         if tuple(q_out.shape) != (n, num_heads * dim) or positions.numel() != n or token_seq.numel() != n:
             raise KernelError("qkv_finish: one query row, one position and one sequence index per token is needed")
-        if (tuple(k_cache.shape[1:]) != (num_kv_heads, block_size, dim)
-                or tuple(v_cache.shape[1:]) != (num_kv_heads, block_size, vdim)):
+        if (tuple(k_cache.shape[1:]) != (num_kv_heads, block_size, key_dim)
+                or (v_cache is not None and tuple(v_cache.shape[1:]) != (num_kv_heads, block_size, vdim))):
             raise KernelError("qkv_finish: the cache must be [blocks, kv_heads, block_size, dim] and [.., vdim]")
+        if (v_cache is None) != (vdim == 0):
+            raise KernelError("qkv_finish: rows without values have vdim 0 and no value cache")
+        if k_norm_weight is not None:
+            self._want(k_norm_weight, torch.float32, "k_norm_weight")
+            if k_norm_weight.numel() != num_kv_heads * key_dim:
+                raise KernelError("qkv_finish: the keys' norm weight must hold kv_heads * dim numbers")
+        coef, every = q_temperature if q_temperature is not None else (0.0, 0)
         self._check(self.lib.skv_qkv_finish(
             _ptr(qkv), qkv.shape[1], _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), _ptr(positions), _ptr(token_seq),
             _ptr(block_table), block_table.shape[1], _ptr(q_out), _ptr(k_cache), _ptr(v_cache), n, num_heads,
             num_kv_heads, dim, vdim, block_size, int(value_norm_eps is not None),
-            ctypes.c_float(value_norm_eps or 0.0), int(bool(write_kv)), _stream()), "qkv_finish")
+            ctypes.c_float(value_norm_eps or 0.0), int(bool(write_kv)), int(bool(q_norm)), int(bool(k_norm)),
+            ctypes.c_float(qk_norm_eps), _ptr(k_norm_weight), ctypes.c_float(coef), int(every), int(key_dim),
+            _stream()), "qkv_finish")
 
     def attention_general(self, q, k_cache, v_cache, block_table, positions, token_seq, out, num_heads: int,
                           num_kv_heads: int, dim: int, vdim: int, block_size: int, scale: float, window: int = 0,
-                          r1=None, r2=None, gate=None, gate_stride: int = 0):
-        """Attention with run-time head sizes (keys ``dim``, values ``vdim``), a warp per (token, head), float math.
+                          r1=None, r2=None, gate=None, gate_stride: int = 0, softcap: float = 0.0,
+                          gate_per_element: bool = False):
+        """(``softcap`` c > 0: scores become ``c * tanh(score / c)``.  ``gate_per_element``: the gate holds a logit for
+        every output number, token t, head h, number d at ``[t * gate_stride + h * vdim + d]``.)
+        Attention with run-time head sizes (keys ``dim``, values ``vdim``), a warp per (token, head), float math.
         ``r1``, ``r2`` (float32 per head): ``r1 * ln(1 + r2 * distance)`` is taken off each score.  ``gate``
         (float32, the logit of token t and head h at ``[t * gate_stride + h]``): the head's output times its sigmoid.
         ``out`` may be wider than ``heads * vdim``; the further columns are set to zero."""
@@ -478,7 +519,8 @@ class Kernels:
                 self._want(value, torch.float32, name)
                 if value.numel() != num_heads:
                     raise KernelError(f"attention_general: {name} must hold one number per head")
-        if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda or gate_stride < num_heads):
+        if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda
+                                 or gate_stride < num_heads * (vdim if gate_per_element else 1)):
             raise KernelError("attention_general: the gate must be float32 on the GPU, a row at least heads wide")
         n = q.shape[0]
         if tuple(q.shape) != (n, num_heads * dim) or out.shape[0] != n or out.shape[1] < num_heads * vdim:
@@ -486,7 +528,115 @@ class Kernels:
         self._check(self.lib.skv_attention_general(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(positions),
             _ptr(token_seq), _ptr(out), n, num_heads, num_kv_heads, dim, vdim, block_size, ctypes.c_float(scale),
-            window, _ptr(r1), _ptr(r2), _ptr(gate), gate_stride, out.shape[1], _stream()), "attention_general")
+            window, _ptr(r1), _ptr(r2), _ptr(gate), gate_stride, out.shape[1], ctypes.c_float(softcap),
+            int(bool(gate_per_element)), _stream()), "attention_general")
+
+    def rmsnorm_add(self, y, gamma, eps: float, x, next_gamma=None, next_eps: float = 0.0, next_out=None):
+        """x += rmsnorm(y) * gamma on float32 rows (the norm after a sublayer); with ``next_gamma`` and ``next_out``
+        (compute dtype) also ``next_out = rmsnorm(new x) * next_gamma``, the input of the sublayer after it."""
+        self._want(y, torch.float32, "y"); self._want(x, torch.float32, "x"); self._want(gamma, torch.float32, "gamma")
+        n, hidden = x.shape
+        if tuple(y.shape) != (n, hidden) or gamma.numel() != hidden:
+            raise KernelError("rmsnorm_add: shapes do not agree")
+        if next_out is not None:
+            self._want(next_out, self.dtype, "next_out"); self._want(next_gamma, torch.float32, "next_gamma")
+            if tuple(next_out.shape) != (n, hidden) or next_gamma.numel() != hidden:
+                raise KernelError("rmsnorm_add: the next norm's shapes do not agree")
+        self._check(self.lib.skv_rmsnorm_add(_ptr(y), _ptr(gamma), ctypes.c_float(eps), _ptr(x), _ptr(next_gamma),
+                                             ctypes.c_float(next_eps), _ptr(next_out), n, hidden, _stream()), "rmsnorm_add")
+
+    def token_side(self, x, ids, table, offset: int, dim: int, gate_w, proj_w, norm_w, eps: float, next_gamma=None,
+                   next_eps: float = 0.0, next_out=None):
+        """An input that depends on the token, added to the float32 stream: ``e = table[id, offset:offset + dim]``,
+        ``g = gelu_tanh(gate_w . x) * e``, ``y = proj_w . g``, ``x += rmsnorm(y) * norm_w``; ``next_*`` as in
+        ``rmsnorm_add``."""
+        self._want(x, torch.float32, "x"); self._want(ids, torch.int32, "ids"); self._want(table, self.dtype, "table")
+        self._want(gate_w, self.dtype, "gate_w"); self._want(proj_w, self.dtype, "proj_w")
+        self._want(norm_w, torch.float32, "norm_w")
+        n, hidden = x.shape
+        if (ids.numel() != n or tuple(gate_w.shape) != (dim, hidden) or tuple(proj_w.shape) != (hidden, dim)
+                or norm_w.numel() != hidden or table.dim() != 2):
+            raise KernelError("token_side: shapes do not agree")
+        if next_out is not None:
+            self._want(next_out, self.dtype, "next_out"); self._want(next_gamma, torch.float32, "next_gamma")
+            if tuple(next_out.shape) != (n, hidden) or next_gamma.numel() != hidden:
+                raise KernelError("token_side: the next norm's shapes do not agree")
+        self._check(self.lib.skv_token_side(
+            _ptr(x), _ptr(ids), _ptr(table), table.shape[1], int(offset), int(dim), table.shape[0], _ptr(gate_w),
+            _ptr(proj_w), _ptr(norm_w), ctypes.c_float(eps), _ptr(next_gamma), ctypes.c_float(next_eps), _ptr(next_out),
+            n, hidden, _stream()), "token_side")
+
+    def headwise_linear(self, x, w, out, heads: int, zero_pad: bool = False):
+        """``out[t, h, :] = w[h] . x[t, h, :]`` with ``w`` ``[heads, out_dim, in_dim]`` in the compute dtype; ``x`` and
+        ``out`` are 2-D, float32 or the compute dtype, head h at columns ``h * in_dim`` and ``h * out_dim`` (rows may be
+        wider; ``zero_pad`` sets what lies beyond an out row's heads to zero).  Sums are float32."""
+        self._want(w, self.dtype, "w")
+        for name, tensor in (("x", x), ("out", out)):
+            if not tensor.is_cuda or tensor.dtype not in (torch.float32, self.dtype) or tensor.dim() != 2 \
+                    or tensor.stride(1) != 1:
+                raise KernelError(f"headwise_linear: {name} must be a 2-D CUDA tensor, float32 or the compute dtype")
+        if w.dim() != 3 or w.shape[0] != heads:
+            raise KernelError("headwise_linear: the weight must be [heads, out_dim, in_dim]")
+        out_dim, in_dim = w.shape[1], w.shape[2]
+        n = x.shape[0]
+        if out.shape[0] != n or x.shape[1] < heads * in_dim or out.shape[1] < heads * out_dim:
+            raise KernelError("headwise_linear: a row is shorter than its heads")
+        self._check(self.lib.skv_headwise_linear(
+            _ptr(x), int(x.dtype == torch.float32), x.stride(0), _ptr(w), _ptr(out), int(out.dtype == torch.float32),
+            out.stride(0), n, heads, in_dim, out_dim, int(bool(zero_pad)), _stream()), "headwise_linear")
+
+    def _recurrent_batch(self, step_meta, state, channels: int, taps: int, name: str):
+        positions, token_seq, cu_q, slot_ids = step_meta
+        for label, tensor in (("positions", positions), ("token_seq", token_seq), ("cu_q", cu_q), ("slot_ids", slot_ids)):
+            self._want(tensor, torch.int32, label)
+        self._want(state, torch.float32, "state")
+        if state.dim() != 2 or state.shape[1] < (2 + taps) * channels or cu_q.numel() != slot_ids.numel() + 1:
+            raise KernelError(f"{name}: the state must be [slots, (2 + taps) * channels or wider] float32")
+        return (_ptr(positions), _ptr(token_seq), _ptr(cu_q), _ptr(slot_ids), _ptr(state), state.shape[1])
+
+    def rglru_conv(self, yx, x_offset: int, x_bias, conv_w, conv_b, u, step_meta, state):
+        """The recurrent branch's causal convolution per channel: ``u[t] = conv_b + sum_k conv_w[:, k] * xb[t - (taps-1-k)]``
+        with ``xb = yx[:, x_offset:x_offset + C] + x_bias``; inputs before this step come from ``state`` (float32
+        ``[slots, (2 + taps) * C]``), positions before a sequence's start are zero.  ``step_meta``: the step's
+        ``(positions, token_seq, cu_q, slot_ids)``."""
+        self._want(yx, torch.float32, "yx"); self._want(u, torch.float32, "u")
+        for label, tensor in (("x_bias", x_bias), ("conv_w", conv_w), ("conv_b", conv_b)):
+            self._want(tensor, torch.float32, label)
+        n, channels = u.shape
+        taps = conv_w.shape[1]
+        if yx.shape[0] != n or tuple(conv_w.shape) != (channels, taps) or x_bias.numel() != channels or conv_b.numel() != channels:
+            raise KernelError("rglru_conv: shapes do not agree")
+        self._check(self.lib.skv_rglru_conv(
+            _ptr(yx), yx.shape[1], int(x_offset), _ptr(x_bias), _ptr(conv_w), _ptr(conv_b), _ptr(u), n, channels, taps,
+            *self._recurrent_batch(step_meta, state, channels, taps, "rglru_conv"), _stream()), "rglru_conv")
+
+    def rglru_gates(self, gates, u, yx, y_bias, r_bias, i_bias, lam, part: int):
+        """In place: ``gates`` (float32 ``[tokens, 2C]``, per part of ``part`` channels its r rows then its i rows, as
+        ``headwise_linear`` leaves them) becomes the decay ``a = exp(-8 sigmoid(r + r_bias) softplus(lam))`` and the driven
+        input ``sqrt(1 - a^2) sigmoid(i + i_bias) u``; ``yx[:, :C]`` becomes ``gelu_tanh(yx[:, :C] + y_bias)``."""
+        self._want(gates, torch.float32, "gates"); self._want(u, torch.float32, "u"); self._want(yx, torch.float32, "yx")
+        for label, tensor in (("y_bias", y_bias), ("r_bias", r_bias), ("i_bias", i_bias), ("lam", lam)):
+            self._want(tensor, torch.float32, label)
+        n, channels = u.shape
+        if tuple(gates.shape) != (n, 2 * channels) or yx.shape[0] != n or any(
+                t.numel() != channels for t in (y_bias, r_bias, i_bias, lam)):
+            raise KernelError("rglru_gates: shapes do not agree")
+        self._check(self.lib.skv_rglru_gates(_ptr(gates), _ptr(u), _ptr(yx), yx.shape[1], _ptr(y_bias), _ptr(r_bias),
+                                             _ptr(i_bias), _ptr(lam), n, channels, int(part), _stream()), "rglru_gates")
+
+    def rglru_scan(self, gates, yx, x_offset: int, x_bias, out, part: int, taps: int, step_meta, state):
+        """``S_t = a_t S_(t-1) + driven_t`` along each sequence's tokens of this step, from and to ``state``;
+        ``out[t, :C] = S_t * yx[t, :C]`` in the compute dtype; the convolution's last inputs go to ``state`` too."""
+        self._want(gates, torch.float32, "gates"); self._want(yx, torch.float32, "yx")
+        self._want(out, self.dtype, "out"); self._want(x_bias, torch.float32, "x_bias")
+        n, channels = gates.shape[0], gates.shape[1] // 2
+        n_seqs = step_meta[3].numel()
+        if yx.shape[0] != n or out.shape[0] != n or out.shape[1] < channels or x_bias.numel() != channels:
+            raise KernelError("rglru_scan: shapes do not agree")
+        self._check(self.lib.skv_rglru_scan(
+            _ptr(gates), _ptr(yx), yx.shape[1], int(x_offset), _ptr(x_bias), _ptr(out), out.shape[1], n_seqs, channels,
+            int(part), int(taps), *self._recurrent_batch(step_meta, state, channels, taps, "rglru_scan"), _stream()),
+            "rglru_scan")
 
     def scale_inplace(self, x, factor: float):
         self._want(x, torch.float32, "x")

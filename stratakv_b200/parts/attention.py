@@ -12,7 +12,10 @@ A spec may switch on further mechanisms (``parts/spec.py::AttentionSpec``): bias
 of another width than keys, an RMS norm on every value head before it is cached, a bias on the scores by the
 logarithm of the distance, and a gate per head on the output.  Such a mixer projects ``[q | k | v | gate]`` at
 once, finishes the rows in ``qkv_finish`` (biases, value norm, cache write) and attends with the kernels
-that carry the bias and the gate (``csrc/attention_general.cu``).
+that carry the bias and the gate (``csrc/attention_general.cu``).  Further switches of that path: a unit norm on
+every query and key head, a temperature on the queries that grows with the position, a cap on the scores
+(``c * tanh(score / c)``), a gate for every output number instead of one per head, and a mixer without key and value
+projections that attends over the cache entry another layer's run wrote.
 """
 from __future__ import annotations
 
@@ -58,18 +61,30 @@ def wants_more_pieces(n_seqs: int, blocks_per_seq: int, max_ctx: int, cluster_sp
             and decode_splits(n_seqs, blocks_per_seq, max_ctx, sms) >= 2 * cluster_splits)
 
 
+def _residual_mode(step):
+    """The epilogue of a mixer's last projection: add to the stream, or store into a branch buffer."""
+    return _ops.MODE_STORE_F32 if getattr(step, "store_branch", False) else _ops.MODE_ADD_F32
+
+
+def _residual_stats(step):
+    return None if getattr(step, "store_branch", False) else step.residual_stats
+
+
 class PagedAttention(Mixer):
     graph_safe = True
     folds_norm = True
+    stores_branch = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         if spec.num_heads % spec.num_kv_heads != 0:
             raise ValueError("attention: heads must be a multiple of kv heads")
         self.q_dim = spec.num_heads * spec.head_dim
-        self.kv_dim = spec.num_kv_heads * spec.head_dim
-        self.v_dim = spec.num_kv_heads * spec.value_dim
+        self.kv_dim = 0 if spec.shares_kv else spec.num_kv_heads * spec.head_dim
+        self.v_dim = 0 if spec.shares_kv else spec.num_kv_heads * spec.value_dim
         self.ctx_dim = spec.num_heads * spec.value_dim
+        if spec.gate_per_element and not spec.gate_weight:
+            raise ValueError("attention: a gate per output number needs a gate weight")
         if spec.extended:
             if spec.position is not None:
                 raise ValueError("attention: the extended mechanisms are built without a rotation")
@@ -80,7 +95,8 @@ class PagedAttention(Mixer):
                                  "(rows of 16 bytes are needed: a multiple of 8); float32 takes any size")
             # the attention output's rows, padded so that the output projection reads whole 16 bytes
             self.ctx_width = -(-self.ctx_dim // 8) * 8
-            gate_rows = spec.num_heads if spec.gate_weight else 0
+            gate_rows = (self.ctx_dim if spec.gate_per_element else spec.num_heads) if spec.gate_weight else 0
+            self.gate_rows = gate_rows
             self.gate_offset = self.q_dim + self.kv_dim + self.v_dim
             self.fused_width = -(-(self.gate_offset + gate_rows) // 8) * 8
             self.position = None
@@ -100,9 +116,10 @@ class PagedAttention(Mixer):
         q_dim, kv_dim = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
         v_dim, ctx_dim = spec.num_kv_heads * spec.value_dim, spec.num_heads * spec.value_dim
         wanted = {spec.q_weight: TensorRequest((q_dim, spec.hidden_size)),
-                  spec.k_weight: TensorRequest((kv_dim, spec.hidden_size)),
-                  spec.v_weight: TensorRequest((v_dim, spec.hidden_size)),
                   spec.o_weight: TensorRequest((spec.hidden_size, ctx_dim))}
+        if not spec.shares_kv:
+            wanted[spec.k_weight] = TensorRequest((kv_dim, spec.hidden_size))
+            wanted[spec.v_weight] = TensorRequest((v_dim, spec.hidden_size))
         for name, width in ((spec.q_bias, q_dim), (spec.k_bias, kv_dim), (spec.v_bias, v_dim)):
             if name:
                 wanted[name] = TensorRequest((width,))
@@ -110,7 +127,8 @@ class PagedAttention(Mixer):
             wanted[spec.distance_bias.r1] = TensorRequest((spec.num_heads,), "positive")
             wanted[spec.distance_bias.r2] = TensorRequest((spec.num_heads,), "positive")
         if spec.gate_weight:
-            wanted[spec.gate_weight] = TensorRequest((spec.num_heads, spec.hidden_size))
+            wanted[spec.gate_weight] = TensorRequest((ctx_dim if spec.gate_per_element else spec.num_heads,
+                                                      spec.hidden_size))
         return wanted
 
     @classmethod
@@ -121,7 +139,8 @@ class PagedAttention(Mixer):
 
     def bind(self, tensors):
         s = self.spec
-        names = [s.q_weight, s.k_weight, s.v_weight] + ([s.gate_weight] if s.extended and s.gate_weight else [])
+        names = ([s.q_weight] + ([] if s.shares_kv else [s.k_weight, s.v_weight])
+                 + ([s.gate_weight] if s.extended and s.gate_weight else []))
         parts = [self.rt.upload(tensors[name]) for name in names]
         if s.extended:
             rows = sum(part.shape[0] for part in parts)
@@ -155,7 +174,8 @@ class PagedAttention(Mixer):
         """True if the kernels that are compiled for one head size can serve this mixer: bfloat16, keys and values
         of one width that a library can be built for, and a distance bias (if any) that fits a table."""
         s = self.spec
-        return (self.rt.dtype == torch.bfloat16 and s.value_dim == s.head_dim and s.head_dim % 16 == 0
+        return (not s.needs_general_kernels
+                and self.rt.dtype == torch.bfloat16 and s.value_dim == s.head_dim and s.head_dim % 16 == 0
                 and s.head_dim <= 256 and self.rt.device.type == "cuda"
                 and (not s.distance_bias or s.window > 0 or s.distance_bias.max_distance > 0))
 
@@ -172,21 +192,25 @@ class PagedAttention(Mixer):
         if step.is_decode and self._specialised():
             ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
             if self._decode_fused(step, fused, ctx, k_cache, v_cache, table, writes_cache):
-                ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
+                ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
                 return
         q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
+        temperature = (s.q_temperature.coef, s.q_temperature.every) if s.q_temperature else None
         ops.qkv_finish(fused, q, k_cache, v_cache, step.positions, step.token_seq, table, s.num_heads,
                        s.num_kv_heads, s.head_dim, s.value_dim, step.cache.block_size, self.q_bias, self.k_bias,
-                       self.v_bias, s.value_norm_eps, writes_cache)
+                       self.v_bias, s.value_norm_eps, writes_cache and not s.shares_kv,
+                       q_norm=s.qk_norm_eps is not None, k_norm=s.qk_norm_eps is not None,
+                       qk_norm_eps=s.qk_norm_eps or 0.0, q_temperature=temperature)
         ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
         gate = fused[:, self.gate_offset:] if s.gate_weight else None
         if self._specialised() and self._attend_specialised(step, q, ctx, k_cache, v_cache, table, gate):
-            ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
+            ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
             return
         ops.attention_general(q, k_cache, v_cache, table, step.positions, step.token_seq, ctx, s.num_heads,
                               s.num_kv_heads, s.head_dim, s.value_dim, step.cache.block_size, s.scale, s.window,
-                              self.r1, self.r2, gate, self.fused_width)
-        ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
+                              self.r1, self.r2, gate, self.fused_width, softcap=s.softcap,
+                              gate_per_element=s.gate_per_element)
+        ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
 
     def _decode_fused(self, step, fused, ctx, k_cache, v_cache, table, writes_cache) -> bool:
         """One token a sequence, in one kernel straight from the fused projection: biases, value norm, cache write,
@@ -263,7 +287,7 @@ class PagedAttention(Mixer):
             qkv = rt.workspace.get("qkv", (n, self.q_dim + 2 * self.kv_dim), torch.float32)
             ops.linear(h, self.w_qkv, qkv, _ops.MODE_STORE_F32)
             self.attend(step, qkv, ctx, cache_entry, writes_cache)
-        ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
+        ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
 
     def attend(self, step, qkv, ctx, cache_entry, writes_cache=True):
         """From the float32 q|k|v rows of the step's tokens to the attention output ``ctx`` (compute dtype):

@@ -121,6 +121,10 @@ class StepBatch:
     scratch: Dict[str, torch.Tensor] = field(default_factory=dict)
     residual_stats: Any = None         # residual.ResidualStats when norms may be folded into projections
     norm_after_layer: Any = None       # then: the foldable norm that reads the stream after the running layer
+    next_layer_norm: Any = None        # the first norm of the layer that runs next (None after the last)
+    # True while a part is handed a scratch buffer in place of the stream and is to STORE its result there instead
+    # of adding it (an arrangement that norms a sublayer's output sets it for parts with ``stores_branch``)
+    store_branch: bool = False
 
     @property
     def is_decode(self) -> bool:
@@ -136,6 +140,9 @@ class Part:
     # (a mixer, a feed-forward) takes them as its input and keeps ``step.residual_stats`` up to date
     # when it adds to the stream.  The arrangement asks before it uses either.
     folds_norm = False
+    # True if the part (a mixer, a feed-forward) looks at ``step.store_branch`` and then stores its result into the
+    # buffer it is given instead of adding to it.  For a part without it the arrangement hands over zeros.
+    stores_branch = False
 
     def __init__(self, spec, runtime: Runtime):
         self.spec = spec

@@ -6,6 +6,8 @@ both branches.  Another arrangement is one more function registered under its na
 """
 from __future__ import annotations
 
+import torch
+
 from .registry import part_class, register_arrangement
 
 
@@ -88,5 +90,76 @@ def parallel(layer: Layer, step, x, entry) -> None:
         stats.invalidate()
 
 
+def _fusable(norm):
+    """True if the kernels that add to the stream can also apply this norm to their result (a plain RMS norm)."""
+    return norm is not None and getattr(norm.spec, "kind", None) == "rmsnorm" and hasattr(norm, "gamma")
+
+
+def _branch(part, step, h, shape, *cache_args):
+    """Run a mixer or feed-forward into a float32 scratch buffer instead of the stream and return the buffer."""
+    rt = part.rt
+    out = rt.workspace.get("branch", shape, torch.float32)
+    if part.stores_branch:
+        step.store_branch = True
+        try:
+            part.forward(step, h, out, *cache_args)
+        finally:
+            step.store_branch = False
+    else:                                           # the part only knows how to add: hand it zeros
+        out.zero_()
+        part.forward(step, h, out, *cache_args)
+    return out
+
+
+def sandwich(layer: Layer, step, x, entry) -> None:
+    """``x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x)))`` and then the layer's ``token_input``, if it has
+    one.  The norms after the sublayers are the extras ``mixer_post_norm`` and ``ffn_post_norm``; a layer may have no
+    feed-forward.  The kernel that adds a normed branch to the stream also applies the norm that reads the stream
+    next (this layer's second, or the next layer's first), which the next reader then finds in ``step.scratch``."""
+    post_mixer, post_ffn = layer.extra.get("mixer_post_norm"), layer.extra.get("ffn_post_norm")
+    side = layer.extra.get("token_input")
+    if layer.mixer_norm is None or layer.mixer is None or post_mixer is None:
+        raise ValueError("the sandwich arrangement needs a norm, a mixer and a norm after it")
+    if layer.ffn is not None and (layer.ffn_norm is None or post_ffn is None):
+        raise ValueError("the sandwich arrangement needs a norm before and after its feed-forward")
+    stats = step.residual_stats
+    if stats is not None:
+        stats.expect(None)                          # nothing here folds a norm into a projection
+    rt = layer.mixer.rt
+    ops = rt.kernels()
+
+    def normed_ahead(norm, name):
+        """The buffer for ``norm`` applied by the kernel in front, or None where that kernel cannot."""
+        return rt.workspace.get(name, tuple(x.shape), rt.dtype) if _fusable(norm) else None
+
+    def add_normed(branch, post, norm_ahead, name):
+        ahead = normed_ahead(norm_ahead, name)
+        ops.rmsnorm_add(branch, post.gamma, post.spec.eps, x,
+                        next_gamma=norm_ahead.gamma if ahead is not None else None,
+                        next_eps=norm_ahead.spec.eps if ahead is not None else 0.0, next_out=ahead)
+        return ahead
+
+    prepared = step.scratch.pop("normed_ahead", None)
+    h = prepared[1] if prepared is not None and prepared[0] is layer.mixer_norm else layer.mixer_norm.forward(x)
+    branch = _branch(layer.mixer, step, h, tuple(x.shape), entry.cache, entry.writes_cache)
+    last = layer.ffn is None and side is None
+    ahead_norm = layer.ffn_norm if layer.ffn is not None else (step.next_layer_norm if last else None)
+    ahead = add_normed(branch, post_mixer, ahead_norm, "normed" if layer.ffn is not None else "normed_next")
+    if layer.ffn is not None:
+        h = ahead if ahead is not None else layer.ffn_norm.forward(x)
+        branch = _branch(layer.ffn, step, h, tuple(x.shape))
+        ahead_norm = step.next_layer_norm if side is None else None
+        ahead = add_normed(branch, post_ffn, ahead_norm, "normed_next")
+    if side is not None:
+        ahead_norm = step.next_layer_norm
+        ahead = normed_ahead(ahead_norm, "normed_next")
+        side.forward(step, x, ahead_norm if ahead is not None else None, ahead)
+    if ahead is not None and ahead_norm is not None:
+        step.scratch["normed_ahead"] = (ahead_norm, ahead)
+    if stats is not None:
+        stats.invalidate()
+
+
 register_arrangement("pre_norm", pre_norm)
+register_arrangement("sandwich", sandwich)
 register_arrangement("parallel", parallel)

@@ -17,8 +17,8 @@ from .registry import register_ffn
 
 def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """``[F, H]`` gate and up -> ``[2F', H]`` with rows (gate 8t..8t+7, up 8t..8t+7) per tile ``t``.
-    ``F'`` is ``F`` rounded up to a multiple of 8; the added rows are zero (they produce
-    ``act(0) * 0 = 0`` and meet zero columns of the down projection)."""
+    ``F'`` is ``F`` rounded up to a multiple of 8; the added rows are zero (whatever the
+    activation makes of them meets zero columns of the down projection)."""
     rows, cols = gate.shape
     if rows % 8 != 0:
         pad = 8 - rows % 8
@@ -29,9 +29,19 @@ def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return tiles.reshape(2 * rows, cols).contiguous()
 
 
+def _residual_mode(step):
+    """The epilogue of the last projection: add to the stream, or store into a branch buffer."""
+    return _ops.MODE_STORE_F32 if getattr(step, "store_branch", False) else _ops.MODE_ADD_F32
+
+
+def _residual_stats(step):
+    return None if getattr(step, "store_branch", False) else getattr(step, "residual_stats", None)
+
+
 class GatedMlp(FeedForward):
     graph_safe = True
     folds_norm = True
+    stores_branch = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -63,8 +73,9 @@ class GatedMlp(FeedForward):
         s, rt = self.spec, self.rt
         ops = rt.kernels()
         z = rt.workspace.get("ffn_hidden", (h.shape[0], self.padded), rt.dtype)
-        ops.linear(h, self.w_gate_up, z, _ops.MODE_GATED, s.activation)
-        ops.linear(z, self.w_down, x, _ops.MODE_ADD_F32, stats=getattr(step, "residual_stats", None))
+        ops.linear(h, self.w_gate_up, z, _ops.MODE_GATED, s.activation,
+                   activation_param=getattr(s, "activation_param", 0.0))
+        ops.linear(z, self.w_down, x, _residual_mode(step), stats=_residual_stats(step))
 
 
 class Mlp(FeedForward):
@@ -72,6 +83,7 @@ class Mlp(FeedForward):
     projection (``ops.MODE_ACT``), the residual sum that of the down projection."""
     graph_safe = True
     folds_norm = True
+    stores_branch = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -102,7 +114,7 @@ class Mlp(FeedForward):
         ops = rt.kernels()
         z = rt.workspace.get("ffn_hidden", (h.shape[0], self.padded), rt.dtype)
         ops.linear(h, self.w_up, z, _ops.MODE_ACT, s.activation)
-        ops.linear(z, self.w_down, x, _ops.MODE_ADD_F32, stats=getattr(step, "residual_stats", None))
+        ops.linear(z, self.w_down, x, _residual_mode(step), stats=_residual_stats(step))
 
 
 register_ffn("gated_mlp", GatedMlp)

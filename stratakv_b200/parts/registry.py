@@ -9,7 +9,8 @@ from __future__ import annotations
 from typing import Dict
 
 _KINDS: Dict[str, Dict[str, type]] = {"mixer": {}, "ffn": {}, "norm": {}, "position": {},
-                                      "arrangement": {}, "embedding": {}, "head": {}}
+                                      "arrangement": {}, "embedding": {}, "head": {},
+                                      "token_input": {}}
 
 
 def register_part(role: str, kind: str, cls) -> None:
@@ -25,6 +26,7 @@ def register_position(kind, cls): register_part("position", kind, cls)
 def register_arrangement(kind, fn): register_part("arrangement", kind, fn)
 def register_embedding(kind, cls): register_part("embedding", kind, cls)
 def register_head(kind, cls): register_part("head", kind, cls)
+def register_token_input(kind, cls): register_part("token_input", kind, cls)
 
 
 def part_class(role: str, kind: str):

@@ -41,13 +41,27 @@ class DistanceBiasSpec:
 
 
 @dataclass(frozen=True)
+class QueryTemperatureSpec:
+    """Queries grow with the position: those at position p are multiplied by
+    ``1 + coef * ln(floor((p + 1) / every) + 1)``."""
+    coef: float
+    every: int
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Causal grouped-query attention over a paged cache (``src/layers/attention.cpp:153-342``).
 
     The fields after ``window`` are mechanisms that a design may add, each off by default: a value head
     size of its own (``v_head_dim``), biases on the three projections, an RMS norm without weight on every
     value head before it is cached (``value_norm_eps``), a bias on the scores by distance, and a gate per
-    head on the attention output, ``sigmoid(h . gate_weight[head])``, read from the mixer's own input."""
+    head on the attention output, ``sigmoid(h . gate_weight[head])``, read from the mixer's own input
+    (``gate_per_element``: a gate for every number of the output, ``gate_weight`` ``[heads * value size, hidden]``).
+    ``qk_norm_eps``: every query and key head is divided by its root mean square (no weight) before the key is
+    cached.  ``q_temperature``: see ``QueryTemperatureSpec``.  ``softcap`` c > 0: scores become
+    ``c * tanh(score / c)`` before the softmax.  ``shares_kv``: the mixer has no key and value projections and
+    attends over the cache entry that another layer's run wrote (its schedule entry names that entry and does
+    not write it)."""
     hidden_size: int
     num_heads: int
     num_kv_heads: int
@@ -67,6 +81,11 @@ class AttentionSpec:
     value_norm_eps: Optional[float] = None
     distance_bias: Optional[DistanceBiasSpec] = None
     gate_weight: Optional[str] = None     # [num_heads, hidden_size]
+    gate_per_element: bool = False
+    qk_norm_eps: Optional[float] = None
+    q_temperature: Optional[QueryTemperatureSpec] = None
+    softcap: float = 0.0
+    shares_kv: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -76,7 +95,80 @@ class AttentionSpec:
     def extended(self) -> bool:
         """True if any mechanism beyond rotated, unbiased queries, keys and values of one width is in use."""
         return bool(self.v_head_dim and self.v_head_dim != self.head_dim or self.q_bias or self.k_bias
-                    or self.v_bias or self.value_norm_eps is not None or self.distance_bias or self.gate_weight)
+                    or self.v_bias or self.value_norm_eps is not None or self.distance_bias or self.gate_weight
+                    or self.qk_norm_eps is not None or self.q_temperature or self.softcap or self.shares_kv)
+
+    @property
+    def needs_general_kernels(self) -> bool:
+        """True if a mechanism is in use that only the kernels with run-time head sizes implement."""
+        return bool(self.qk_norm_eps is not None or self.q_temperature or self.softcap or self.shares_kv
+                    or self.gate_per_element)
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are up-projections of one compressed vector per position.
+
+    ``c = rmsnorm(Wdkv h) * latent_norm`` (``latent_dim`` numbers) is all the cache keeps; head h has
+    ``k = Wuk[h] c`` (``head_dim``) and ``v = Wuv[h] c`` (``v_head_dim``), ``score = (q . k) * scale``, no position
+    encoding; ``x += Wo (heads' outputs)``."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    v_head_dim: int
+    latent_dim: int
+    scale: float
+    eps: float                       # of the latent's norm
+    q_weight: str                    # [heads * head_dim, hidden]
+    down_weight: str                 # [latent_dim, hidden]
+    latent_norm: str                 # [latent_dim]
+    k_up_weight: str                 # [heads * head_dim, latent_dim]
+    v_up_weight: str                 # [heads * v_head_dim, latent_dim]
+    o_weight: str                    # [hidden, heads * v_head_dim]
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class RgLruSpec:
+    """A recurrent block around a real-gated linear recurrent unit (the Griffin block): two branches of
+    ``channels`` numbers, ``y = gelu_tanh(Wy h + by)`` and ``u = conv(Wx h + bx)`` (causal, per channel, ``taps``
+    wide); per equal part of the channels ``r = sigmoid(Ra u + ba)``, ``i = sigmoid(Ri u + bi)``;
+    ``a = exp(-8 r softplus(lam))``, ``S <- a S + sqrt(1 - a^2) i u``; ``x += Wo (S * y)``."""
+    hidden_size: int
+    channels: int
+    parts: int                       # the gates' matrices are block-diagonal with this many blocks
+    taps: int
+    y_weight: str
+    y_bias: str
+    x_weight: str
+    x_bias: str
+    conv_weight: str                 # [channels, taps], the last column weighs the current token
+    conv_bias: str
+    r_weight: str                    # [parts, channels / parts, channels / parts], rows are outputs
+    r_bias: str                      # [parts, channels / parts]
+    i_weight: str
+    i_bias: str
+    decay: str                       # lam, [channels]
+    o_weight: str
+    kind: str = "rglru"
+
+
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """An input that depends on the token, added to the stream at the end of a layer:
+    ``e = table[token, offset : offset + dim]``, ``g = gelu_tanh(gate x) * e``, ``y = proj g``,
+    ``x += rmsnorm(y) * norm`` (a plain-weight RMS norm with ``eps``).  ``table`` is one tensor for all layers."""
+    hidden_size: int
+    vocab_size: int
+    dim: int
+    offset: int
+    table_width: int
+    eps: float
+    table: str
+    gate_weight: str                 # [dim, hidden]
+    proj_weight: str                 # [hidden, dim]
+    norm_weight: str                 # [hidden]
+    kind: str = "token_side"
 
 
 @dataclass(frozen=True)
@@ -84,11 +176,12 @@ class GatedMlpSpec:
     """``down(act(gate(x)) * up(x))`` (``src/models/transformer_block.cpp:312-325``)."""
     hidden_size: int
     intermediate_size: int
-    activation: str                  # "silu"
+    activation: str                  # "silu", "gelu_tanh", or "swiglu_clamp" (takes ``activation_param``)
     gate_weight: str
     up_weight: str
     down_weight: str
     kind: str = "gated_mlp"
+    activation_param: float = 0.0    # "swiglu_clamp": both branches are clamped to it (ops.PARAMETRIC_ACTIVATIONS)
 
 
 @dataclass(frozen=True)
@@ -110,6 +203,9 @@ class LayerSpec:
     (``src/models/transformer_block.cpp:301-331``).
     ``parallel``: ``h = norm1(x); x += mixer(h) + ffn(h)``: one norm (``mixer_norm``), both branches read its
     output; ``ffn`` may be ``None``.
+    ``sandwich``: ``x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x)))``, then ``token_input`` if the layer
+    has one; the norms after the sublayers are the extras ``mixer_post_norm`` and ``ffn_post_norm``, ``ffn`` (with
+    its two norms) may be ``None``.
 
     The four named places are what that arrangement uses; another arrangement may leave
     some of them ``None`` (a block without a feed-forward, one norm for two branches) and

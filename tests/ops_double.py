@@ -31,13 +31,18 @@ class DoubleKernels:
         inv = 1.0 / torch.sqrt((src * src).mean(dim=-1, keepdim=True) + eps)
         out.copy_((src * inv * gamma).to(out.dtype))
 
-    def linear(self, a, w, out, mode=MODE_STORE, activation="silu", flag=None, stats=None):
+    def linear(self, a, w, out, mode=MODE_STORE, activation="silu", flag=None, stats=None, activation_param=0.0):
         self.calls.append("linear")
         result = a.float() @ w.float().T
         if mode == MODE_GATED:
             tiles = result.view(result.shape[0], -1, 2, 8)
             gate, up = tiles[:, :, 0, :], tiles[:, :, 1, :]
-            out.copy_((gate * torch.sigmoid(gate) * up).reshape(result.shape[0], -1).to(out.dtype))
+            if activation == "swiglu_clamp":
+                gate = gate.clamp(max=activation_param)
+                product = gate * torch.sigmoid(1.702 * gate) * (up.clamp(-activation_param, activation_param) + 1.0)
+            else:
+                product = ACTIVATIONS[activation](gate) * up
+            out.copy_(product.reshape(result.shape[0], -1).to(out.dtype))
         elif mode == MODE_ADD_F32:
             out.add_(result)
         elif mode == MODE_ACT:
@@ -112,27 +117,47 @@ class DoubleKernels:
         out.copy_(x)
 
     def qkv_finish(self, qkv, q_out, k_cache, v_cache, positions, token_seq, block_table, num_heads, num_kv_heads,
-                   dim, vdim, block_size, q_bias=None, k_bias=None, v_bias=None, value_norm_eps=None, write_kv=True):
+                   dim, vdim, block_size, q_bias=None, k_bias=None, v_bias=None, value_norm_eps=None, write_kv=True,
+                   q_norm=False, k_norm=False, qk_norm_eps=0.0, k_norm_weight=None, q_temperature=None, key_dim=0):
         self.calls.append("qkv_finish")
         n = qkv.shape[0]
-        a, b = num_heads * dim, (num_heads + num_kv_heads) * dim
-        q, k, v = qkv[:, :a], qkv[:, a:b], qkv[:, b:b + num_kv_heads * vdim]
-        q = q + q_bias if q_bias is not None else q
-        k = k + k_bias if k_bias is not None else k
-        v = (v + v_bias if v_bias is not None else v).view(n, num_kv_heads, vdim)
-        if value_norm_eps is not None:
-            v = v / torch.sqrt((v * v).mean(dim=-1, keepdim=True) + value_norm_eps)
-        q_out.copy_(q.to(q_out.dtype))
-        if write_kv:
-            k = k.view(n, num_kv_heads, dim)
-            for t in range(n):
-                pos = int(positions[t])
-                block = int(block_table[int(token_seq[t]), pos // block_size])
-                k_cache[block, :, pos % block_size, :] = k[t].to(k_cache.dtype)
+        key_dim = key_dim or dim
+        unit = lambda x, eps: x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
+        a = num_heads * dim
+        q = qkv[:, :a]
+        q = (q + q_bias if q_bias is not None else q).view(n, num_heads, dim)
+        if q_norm:
+            q = unit(q, qk_norm_eps)
+        if q_temperature is not None:
+            coef, every = q_temperature
+            steps = torch.div(positions.long() + 1, every, rounding_mode="floor").float()
+            q = q * (1.0 + coef * torch.log(steps + 1.0))[:, None, None]
+        q_out.copy_(q.reshape(n, a).to(q_out.dtype))
+        if not write_kv:
+            return
+        b = a + num_kv_heads * key_dim
+        k = qkv[:, a:b]
+        k = (k + k_bias if k_bias is not None else k).view(n, num_kv_heads, key_dim)
+        if k_norm:
+            k = unit(k, qk_norm_eps)
+            if k_norm_weight is not None:
+                k = k * k_norm_weight.view(num_kv_heads, key_dim)
+        v = None
+        if vdim > 0:
+            v = qkv[:, b:b + num_kv_heads * vdim]
+            v = (v + v_bias if v_bias is not None else v).view(n, num_kv_heads, vdim)
+            if value_norm_eps is not None:
+                v = unit(v, value_norm_eps)
+        for t in range(n):
+            pos = int(positions[t])
+            block = int(block_table[int(token_seq[t]), pos // block_size])
+            k_cache[block, :, pos % block_size, :] = k[t].to(k_cache.dtype)
+            if v is not None:
                 v_cache[block, :, pos % block_size, :] = v[t].to(v_cache.dtype)
 
     def attention_general(self, q, k_cache, v_cache, block_table, positions, token_seq, out, num_heads, num_kv_heads,
-                          dim, vdim, block_size, scale, window=0, r1=None, r2=None, gate=None, gate_stride=0):
+                          dim, vdim, block_size, scale, window=0, r1=None, r2=None, gate=None, gate_stride=0,
+                          softcap=0.0, gate_per_element=False):
         self.calls.append("attention_general")
         n = q.shape[0]
         group = num_heads // num_kv_heads
@@ -149,10 +174,83 @@ class DoubleKernels:
                 score = (keys[:, h // group, :] @ qh[t, h]) * scale
                 if r1 is not None:
                     score = score - r1[h] * torch.log1p(r2[h] * distance)
+                if softcap > 0.0:
+                    score = softcap * torch.tanh(score / softcap)
                 result = torch.softmax(score, dim=0) @ values[:, h // group, :]
-                if gate is not None:
+                if gate is not None and gate_per_element:
+                    result = result * torch.sigmoid(gate[t, h * vdim:(h + 1) * vdim])
+                elif gate is not None:
                     result = result * torch.sigmoid(gate[t, h])
                 out[t, h * vdim:(h + 1) * vdim] = result.to(out.dtype)
+
+    def rmsnorm_add(self, y, gamma, eps, x, next_gamma=None, next_eps=0.0, next_out=None):
+        self.calls.append("rmsnorm_add")
+        x.add_(y / torch.sqrt((y * y).mean(dim=-1, keepdim=True) + eps) * gamma)
+        if next_out is not None:
+            next_out.copy_((x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + next_eps) * next_gamma).to(next_out.dtype))
+
+    def token_side(self, x, ids, table, offset, dim, gate_w, proj_w, norm_w, eps, next_gamma=None, next_eps=0.0,
+                   next_out=None):
+        self.calls.append("token_side")
+        e = table[ids.long()][:, offset:offset + dim].float()
+        g = torch.nn.functional.gelu(x @ gate_w.float().T, approximate="tanh") * e
+        self.rmsnorm_add(g @ proj_w.float().T, norm_w, eps, x, next_gamma, next_eps, next_out)
+
+    def headwise_linear(self, x, w, out, heads, zero_pad=False):
+        self.calls.append("headwise_linear")
+        n, out_dim, in_dim = x.shape[0], w.shape[1], w.shape[2]
+        parts = x[:, :heads * in_dim].float().view(n, heads, in_dim)
+        if zero_pad:
+            out.zero_()
+        out[:, :heads * out_dim] = torch.einsum("thi,hoi->tho", parts, w.float()).reshape(n, heads * out_dim).to(out.dtype)
+
+    def rglru_conv(self, yx, x_offset, x_bias, conv_w, conv_b, u, step_meta, state):
+        self.calls.append("rglru_conv")
+        positions, token_seq, cu_q, slot_ids = step_meta
+        channels, taps = conv_w.shape
+        for t in range(u.shape[0]):
+            p, s = int(positions[t]), int(token_seq[t])
+            ring = state[int(slot_ids[s]), 2 * channels:(2 + taps) * channels].view(taps, channels)
+            total = conv_b.clone()
+            for k in range(taps):
+                back = taps - 1 - k
+                if p - back < 0:
+                    continue
+                inside = t - back >= int(cu_q[s])
+                value = yx[t - back, x_offset:x_offset + channels] + x_bias if inside else ring[(p - back) % taps]
+                total = total + conv_w[:, k] * value
+            u[t] = total
+
+    def rglru_gates(self, gates, u, yx, y_bias, r_bias, i_bias, lam, part):
+        self.calls.append("rglru_gates")
+        n, channels = u.shape
+        pairs = gates.view(n, channels // part, 2, part)
+        r = torch.sigmoid(pairs[:, :, 0, :] + r_bias.view(-1, part))
+        i = torch.sigmoid(pairs[:, :, 1, :] + i_bias.view(-1, part))
+        a = torch.exp(-8.0 * r * torch.nn.functional.softplus(lam).view(-1, part))
+        driven = torch.sqrt(1.0 - a * a) * i * u.view(n, -1, part)
+        pairs[:, :, 0, :] = a
+        pairs[:, :, 1, :] = driven
+        yx[:, :channels] = torch.nn.functional.gelu(yx[:, :channels] + y_bias, approximate="tanh")
+
+    def rglru_scan(self, gates, yx, x_offset, x_bias, out, part, taps, step_meta, state):
+        self.calls.append("rglru_scan")
+        positions, token_seq, cu_q, slot_ids = step_meta
+        n, channels = gates.shape[0], gates.shape[1] // 2
+        pairs = gates.view(n, channels // part, 2, part)
+        for s in range(slot_ids.numel()):
+            first, last = int(cu_q[s]), int(cu_q[s + 1]) - 1
+            row = state[int(slot_ids[s])]
+            p_first = int(positions[first])
+            S = row[((p_first - 1) & 1) * channels:][:channels].clone() if p_first > 0 else torch.zeros(channels)
+            for t in range(first, last + 1):
+                S = pairs[t, :, 0, :].reshape(-1) * S + pairs[t, :, 1, :].reshape(-1)
+                out[t, :channels] = (S * yx[t, :channels]).to(out.dtype)
+            p_last = p_first + last - first
+            row[(p_last & 1) * channels:][:channels] = S
+            ring = row[2 * channels:(2 + taps) * channels].view(taps, channels)
+            for back in range(min(taps, last - first + 1)):
+                ring[(p_last - back) % taps] = yx[last - back, x_offset:x_offset + channels] + x_bias
 
     def scale_inplace(self, x, factor):
         x.mul_(factor)
