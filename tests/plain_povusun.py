@@ -163,3 +163,28 @@ def forward(cfg, tensors, tokens, return_layers: bool = False):
         after.append(x)
     logits = rms_norm(x, P["final.norm"], eps) @ P["embed"].T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def load_folder(folder):
+    """(config dictionary, tensors as float64) of a model folder; reads the safetensors container itself."""
+    import json
+    import struct
+    from pathlib import Path
+    folder = Path(folder)
+    config = json.loads((folder / "config.json").read_text())
+    raw = (folder / "model.safetensors").read_bytes()
+    (size,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + size])
+    kinds = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "I32": torch.int32}
+    weights = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        begin, end = info["data_offsets"]
+        flat = torch.frombuffer(bytearray(raw[8 + size + begin:8 + size + end]), dtype=kinds[info["dtype"]])
+        weights[name] = flat.reshape(info["shape"]).to(F64)
+    return config, weights
+
+
+def logits_of(config, weights, tokens):
+    return forward(config, weights, tokens)

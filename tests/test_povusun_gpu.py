@@ -1,0 +1,255 @@
+"""The Povusun decoder in the engine against the plain implementation (tests/plain_povusun.py): whole prompts,
+prompts then tokens one by one, prompts in portions down to two tokens, batches of unequal requests with early
+finishers and slots, pages and recurrent states used again, long decoding, the stream after every layer, greedy
+generation through Engine.generate, the command line and the trace runner; in float32 and in bfloat16, on
+configurations that differ in every size."""
+import numpy as np
+import pytest
+import torch
+
+import plain_povusun
+from helpers import random_tokens, run_trace, stored_dtype
+from povusun_models import POVUSUN, make_folder
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+# A position's logits may differ from the plain ones by this fraction of the logits' spread in the root mean square
+# over the vocabulary, and a single logit by four times that.  The test models' attention is peaked and their
+# recurrent layers remember long, so that bfloat16 rounding moves a position by a few hundredths of the spread while
+# a lost cap, gate, state or side input moves one by 0.12 or more (tests/test_povusun.py shows that on the plain
+# implementation).  float32 differs by the order of its sums.
+ROW_NOISE = {"bfloat16": 0.06, "float32": 5e-5}
+
+
+class Folders:
+    def __init__(self, root):
+        self.root, self.made, self.logits = root, {}, {}
+
+    def __getitem__(self, key):
+        name, dtype = key
+        if key not in self.made:
+            self.made[key] = make_folder(self.root / f"{name}_{dtype}", POVUSUN[name], seed=5 + list(POVUSUN).index(name),
+                                         dtype=stored_dtype(dtype))
+        return self.made[key]
+
+    def plain(self, name, dtype, tokens):
+        key = (name, dtype, tuple(tokens))
+        if key not in self.logits:
+            config, weights = plain_povusun.load_folder(self[name, dtype])
+            self.logits[key] = plain_povusun.logits_of(config, weights, list(tokens)).numpy()
+        return self.logits[key]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return Folders(tmp_path_factory.mktemp("povusun"))
+
+
+def engine_for(folder, dtype, max_tokens=2048, block_size=64, **more):
+    from stratakv_b200 import Engine, EngineConfig
+    return Engine.from_folder(folder, EngineConfig(max_tokens=max_tokens, dtype=dtype, block_size=block_size, **more),
+                              verbose=False)
+
+
+def check(got, ref, dtype, what=""):
+    got = got.detach().float().cpu().numpy() if isinstance(got, torch.Tensor) else got
+    assert got.shape == ref.shape, what
+    spread = float(np.asarray(ref, dtype=np.float64).std())
+    difference = got.astype(np.float64) - ref
+    per_position = np.sqrt((difference ** 2).mean(axis=-1))
+    worst = int(per_position.argmax())
+    allowed = ROW_NOISE[dtype] * spread
+    assert per_position[worst] <= allowed, f"{what}: row {worst} is off by {per_position[worst] / spread:.2e} of the spread"
+    assert np.abs(difference).max() <= 4 * allowed, f"{what}: a logit is off by {np.abs(difference).max() / spread:.2e} of the spread"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(POVUSUN))
+def test_whole_prompts(folders, dtype, name):
+    from stratakv_b200 import StepEntry
+    engine = engine_for(folders[name, dtype], dtype)
+    for length in (1, 2, 3, 33, 64, 65, 150, 300):
+        tokens = random_tokens(POVUSUN[name]["vocab"], length, seed=length)
+        slot = engine.open_sequence()
+        got = engine.step([StepEntry(slot, tokens, list(range(length)))])
+        check(got, folders.plain(name, dtype, tokens), dtype, f"{name} whole length {length}")
+        engine.close_sequence(slot)
+    engine.check_flags()
+    assert engine.cache.all_free()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_stream_after_every_layer(folders, dtype):
+    """Layer by layer: the float32 residual stream after each layer against the plain one."""
+    from stratakv_b200 import StepEntry
+    name = "PA"
+    engine = engine_for(folders[name, dtype], dtype)
+    tokens = random_tokens(POVUSUN[name]["vocab"], 70, seed=12)
+    config, weights = plain_povusun.load_folder(folders[name, dtype])
+    _, streams = plain_povusun.forward(config, weights, tokens, return_layers=True)
+    seen = []
+    engine.model.layer_probe = lambda index, x: seen.append(x.detach().cpu().double().clone())
+    slot = engine.open_sequence()
+    engine.step([StepEntry(slot, tokens, [])])
+    engine.model.layer_probe = None
+    assert len(seen) == len(POVUSUN[name]["layers"])
+    for index, (got, ref) in enumerate(zip(seen, streams)):
+        allowed = (3e-5 if dtype == "float32" else 0.04) * float(ref.std())
+        worst = float(torch.sqrt(((got - ref) ** 2).mean(dim=-1)).max())
+        assert worst <= allowed, f"after layer {index} ({POVUSUN[name]['layers'][index]['type']}): {worst / float(ref.std()):.2e} of the spread"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(POVUSUN))
+def test_prompt_then_tokens_one_by_one(folders, dtype, name):
+    """The first tokens of a sequence decoded alone (prompts of 1 and 2), and decoding that starts inside a page,
+    runs over page borders, past every temperature period of the configuration and through the graphs of a step."""
+    from stratakv_b200 import StepEntry
+    engine = engine_for(folders[name, dtype], dtype)
+    for prompt, total in ((1, 40), (2, 10), (50, 140), (120, 330)):
+        tokens = random_tokens(POVUSUN[name]["vocab"], total, seed=total)
+        ref = folders.plain(name, dtype, tokens)
+        slot = engine.open_sequence()
+        got = engine.step([StepEntry(slot, tokens[:prompt], list(range(prompt)))])
+        check(got, ref[:prompt], dtype, f"{name} prompt of {prompt}")
+        for p in range(prompt, total):
+            got = engine.step([StepEntry(slot, [tokens[p]], [0])])
+            check(got, ref[p:p + 1], dtype, f"{name} position {p} decoded after a prompt of {prompt}")
+        engine.close_sequence(slot)
+    engine.check_flags()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(POVUSUN))
+def test_prompts_in_portions(folders, dtype, name):
+    """Portions shorter than the convolution's taps, of two tokens, and ones that end at and after a page's border."""
+    from stratakv_b200 import StepEntry
+    engine = engine_for(folders[name, dtype], dtype)
+    for portions in ((70, 65, 40), (2, 2, 2, 2, 2), (63, 2, 1, 64, 33), (130, 2, 100), (1, 1, 3, 1, 2, 5)):
+        tokens = random_tokens(POVUSUN[name]["vocab"], sum(portions), seed=sum(portions))
+        ref = folders.plain(name, dtype, tokens)
+        slot, at = engine.open_sequence(), 0
+        for count in portions:
+            got = engine.step([StepEntry(slot, tokens[at:at + count], list(range(count)))])
+            check(got, ref[at:at + count], dtype, f"{name} portion {at}..{at + count} of {portions}")
+            at += count
+        engine.close_sequence(slot)
+    engine.check_flags()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(POVUSUN))
+def test_unequal_batches_with_early_finishers_and_reuse(folders, dtype, name):
+    """Two batches one after the other in one engine whose cache just holds one of them: the second takes the
+    slots, pages and recurrent states that the first gave back."""
+    from stratakv_b200 import StepEntry
+    vocab = POVUSUN[name]["vocab"]
+    engine = engine_for(folders[name, dtype], dtype, max_tokens=64 * 12, max_batch=4)
+    for batch, shapes in enumerate((((1, 5), (70, 12), (200, 30), (129, 31)), ((3, 33), (190, 3), (64, 40), (2, 1)))):
+        requests = [random_tokens(vocab, prompt + more, seed=100 * batch + i) for i, (prompt, more) in enumerate(shapes)]
+        refs = [folders.plain(name, dtype, tokens) for tokens in requests]
+        slots = [engine.open_sequence() for _ in requests]
+        got = engine.step([StepEntry(slot, tokens[:prompt], [prompt - 1])
+                           for slot, tokens, (prompt, _) in zip(slots, requests, shapes)])
+        for row, (ref, (prompt, _)) in enumerate(zip(refs, shapes)):
+            check(got[row:row + 1], ref[prompt - 1:prompt], dtype, f"{name} batch {batch} prompt {row}")
+        for step in range(max(more for _, more in shapes)):
+            live = [i for i, (_, more) in enumerate(shapes) if step < more]
+            got = engine.step([StepEntry(slots[i], [requests[i][shapes[i][0] + step]], [0]) for i in live])
+            for row, i in enumerate(live):
+                at = shapes[i][0] + step
+                check(got[row:row + 1], refs[i][at:at + 1], dtype, f"{name} batch {batch} request {i} position {at}")
+            for i in live:
+                if step + 1 == shapes[i][1]:
+                    engine.close_sequence(slots[i])
+        engine.check_flags()
+    assert engine.cache.all_free()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_pages_of_sixteen_and_long_decoding(folders, dtype):
+    """Small pages and 400 tokens one by one: the recurrent state is carried for hundreds of steps and every
+    attention layer reads across twenty-odd pages."""
+    from stratakv_b200 import StepEntry
+    name = "PA"
+    engine = engine_for(folders[name, dtype], dtype, max_tokens=16 * 30, block_size=16, max_batch=1)
+    tokens = random_tokens(POVUSUN[name]["vocab"], 430, seed=77)
+    ref = folders.plain(name, dtype, tokens)
+    slot = engine.open_sequence()
+    got = engine.step([StepEntry(slot, tokens[:30], [29])])
+    check(got, ref[29:30], dtype, "prompt")
+    for p in range(30, 430):
+        got = engine.step([StepEntry(slot, [tokens[p]], [0])])
+        check(got, ref[p:p + 1], dtype, f"position {p}")
+    engine.close_sequence(slot)
+    assert engine.cache.all_free()
+
+
+@pytest.mark.parametrize("name", ["PA", "PC"])
+def test_greedy_generation_through_the_engine(folders, name):
+    """Engine.generate (the scheduler, the graph steps that run ahead of the host, the sampler): every token it
+    chooses is the plain implementation's best or within rounding of it."""
+    dtype = "float32"
+    engine = engine_for(folders[name, dtype], dtype, max_tokens=1024)
+    vocab = POVUSUN[name]["vocab"]
+    prompts = [random_tokens(vocab, n, seed=900 + n) for n in (1, 9, 70)]
+    output = engine.generate(prompts, 24, ignore_eos=True)
+    config, weights = plain_povusun.load_folder(folders[name, dtype])
+    for prompt, sequence in zip(prompts, output.sequences):
+        assert len(sequence) == len(prompt) + 24 and sequence[:len(prompt)] == prompt
+        logits = plain_povusun.logits_of(config, weights, sequence).numpy()
+        for at in range(len(prompt), len(sequence)):
+            row = logits[at - 1]
+            assert row[sequence[at]] >= row.max() - 1e-4 * max(1.0, abs(row.max())), f"{name}: token {at} is not the best"
+    assert engine.cache.all_free()
+
+
+def test_generation_in_bfloat16_repeats_itself(folders):
+    """Generation through graphs and through eager steps chooses the same tokens (recurrent state included)."""
+    name, dtype = "PA", "bfloat16"
+    prompts = [random_tokens(POVUSUN[name]["vocab"], n, seed=40 + n) for n in (5, 31)]
+    outputs = []
+    for graphs in (True, False):
+        engine = engine_for(folders[name, dtype], dtype, max_tokens=512, use_cuda_graphs=graphs)
+        outputs.append(engine.generate(prompts, 20, ignore_eos=True).sequences)
+    assert outputs[0] == outputs[1]
+
+
+def test_command_line_generates_from_a_povusun_folder(folders):
+    """bin/stratakv_cli opens the folder through the registry like every other entry point; greedy, float32."""
+    import subprocess
+    import sys
+    from helpers import ROOT
+    name = "PB"
+    folder = folders[name, "float32"]
+    prompt = random_tokens(POVUSUN[name]["vocab"], 12, seed=8)
+    done = subprocess.run([sys.executable, str(ROOT / "bin" / "stratakv_cli"), "--dtype", "float32", "--temp", "0",
+                           "--ignore-eos", str(folder), "10", *[str(t) for t in prompt]],
+                          capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    sequence = [int(word) for word in done.stdout.split()]
+    assert len(sequence) == 22 and sequence[:12] == prompt
+    config, weights = plain_povusun.load_folder(folder)
+    logits = plain_povusun.logits_of(config, weights, sequence).numpy()
+    for at in range(12, 22):
+        row = logits[at - 1]
+        assert row[sequence[at]] >= row.max() - 1e-4 * max(1.0, abs(row.max()))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_runner_chooses_the_model_by_its_config(folders, dtype, tmp_path):
+    name = "PB"
+    folder = folders[name, dtype]
+    vocab = POVUSUN[name]["vocab"]
+    a, b = random_tokens(vocab, 75, seed=1), random_tokens(vocab, 20, seed=2)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:70], "want": [0, 69]}, {"id": "b", "tokens": b[:18], "want": [17]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[70:71], "want": [0]}, {"id": "b", "tokens": b[18:19], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[71:72], "want": [0]}, {"id": "b", "tokens": b[19:20], "want": [0]}], "end": ["b"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[72:75], "want": [2]}], "end": ["a"]}]
+    logits = run_trace(folder, dtype, steps, tmp_path / "out", max_tokens=256, vocab=vocab)
+    ref_a, ref_b = folders.plain(name, dtype, a), folders.plain(name, dtype, b)
+    check(logits[0], np.stack([ref_a[0], ref_a[69], ref_b[17]]), dtype, "step 0")
+    check(logits[1], ref_a[70:71], dtype, "step 1")
+    check(logits[2], np.stack([ref_a[71], ref_b[19]]), dtype, "step 2")
+    check(logits[3], ref_a[74:75], dtype, "step 3")
