@@ -2,6 +2,8 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
     python bench.py --design zepavik [--layers 8]       (the Zepavik decoder beside Llama at equal layer sizes)
+    python bench.py --design povusun [--layers 8]       (the Povusun decoder beside Llama: mixed layers, and each of its
+                                                         three mixers alone)
 
 The default run has the layer sizes of the TinyLlama-1.1B shape (22 layers,
 hidden 2048, 32 heads, 4 KV heads, head size 64, feed-forward 5632, vocabulary
@@ -162,8 +164,89 @@ DESIGN_SIZES = {
 }
 
 
+def povusun_config(size, layers, vocab, kinds):
+    """A Povusun configuration at a size of DESIGN_SIZES whose layer i has the mixer ``kinds[i % len(kinds)]``: the
+    attention layers with Llama's heads (keys and values of one width, a cap, a temperature), the latent ones with a
+    latent of four heads' width (at most 512), the recurrent ones as wide as the model with a part per query head and
+    four taps; every layer with a feed-forward of Llama's inner width (three matrices, as there) and a token input."""
+    from stratakv_b200.config import PovusunConfig
+    d, made, lender = size["head_dim"], [], None
+    for i in range(layers):
+        kind = kinds[i % len(kinds)]
+        if kind == "attention":
+            mixer = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5,
+                     "softcap": 30.0, "q_temp": {"coef": 0.1, "every": 512}}
+            if lender is not None and i == layers - 2 and len(kinds) > 1:
+                mixer["kv_from"] = lender              # (one layer borrows its keys, as models of the design do)
+            elif lender is None:
+                lender = i
+        elif kind == "latent_attention":
+            mixer = {"heads": size["heads"], "dim": d, "vdim": d, "kv_rank": min(512, 4 * d), "scale": d ** -0.5}
+        else:
+            mixer = {"width": size["hidden"], "blocks": size["heads"], "conv": 4}
+        made.append({"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": size["llama_ff"], "limit": 7.0}})
+    return PovusunConfig.from_dict({"architecture": "Povusun", "vocab": vocab, "width": size["hidden"],
+                                    "norm": {"eps": 1e-5}, "token_side": {"dim": 32}, "layers": made})
+
+
+def povusun_arm(args) -> int:
+    """Prefill and decode of the Povusun decoder beside the Llama decoder at equal layer sizes (random weights): a
+    model that mixes its three kinds of layer, and one of each kind alone, so that each mixer's kernels can be set
+    beside Llama's attention."""
+    import gc
+    import torch
+    from stratakv_b200.config import LlamaConfig
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device")
+        return 1
+    layers, vocab, context, batch = args.layers or 8, 32000, args.context, args.batch
+    steps, warmup = max(args.steps, 1), max(args.warmup, 3)
+    peak = peaks()
+    sizes = {}
+    sampler = ClockSampler()
+    sampler.start()
+    mixes = {"povusun": ("attention", "latent_attention", "rglru"), "attention_only": ("attention",),
+             "latent_only": ("latent_attention",), "rglru_only": ("rglru",)}
+    for name, size in DESIGN_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        configs = {"llama": LlamaConfig.from_dict(dict(
+            TINYLLAMA, hidden_size=size["hidden"], intermediate_size=size["llama_ff"], num_hidden_layers=layers,
+            num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["head_dim"],
+            vocab_size=vocab, max_position_embeddings=context + 64))}
+        for label, kinds in mixes.items():
+            configs[label] = povusun_config(size, layers, vocab, kinds)
+        row = {}
+        for label, config in configs.items():
+            engine = engine_of(config, max(batch * (context + 64), PREFILL_TOKENS + 64), batch)
+            prefill_ms = time_prefill(engine, PREFILL_TOKENS, vocab)
+            decode_ms, launches, _ = time_decode(engine, batch, context - steps - warmup, steps, warmup, vocab)
+            weight_bytes = engine.model.weight_bytes()
+            kv_bytes = batch * context * engine.cache.bytes_per_token()
+            row[label] = {"prefill_tokens_per_s": PREFILL_TOKENS * 1000.0 / prefill_ms, "prefill_ms": prefill_ms,
+                          "decode_tokens_per_s": batch * 1000.0 / decode_ms, "decode_ms_per_step": decode_ms,
+                          "decode_hbm_frac": (weight_bytes + kv_bytes) / (decode_ms * 1e-3) / 1e9 / peak["hbm_gbs"],
+                          "weight_bytes": weight_bytes, "launches_in_timed_steps": launches}
+            del engine
+            gc.collect()
+            torch.cuda.empty_cache()
+        for label in mixes:
+            row[label]["prefill_ratio"] = row[label]["prefill_tokens_per_s"] / row["llama"]["prefill_tokens_per_s"]
+            row[label]["decode_ratio"] = row[label]["decode_tokens_per_s"] / row["llama"]["decode_tokens_per_s"]
+        sizes[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"design": "Povusun", "beside": "LlamaForCausalLM", "layers": layers, "vocab": vocab,
+                      "prefill_tokens": PREFILL_TOKENS, "decode_batch": batch, "context": context, "dtype": "bf16",
+                      "steps": steps, "warmup": warmup,
+                      "data": "synthetic: random N(0,0.02) weights, uniform random token ids", "peaks": peak,
+                      "clocks": clocks, "sizes": sizes}))
+    return 0
+
+
 def design_arm(args) -> int:
     """Prefill and decode of the Zepavik decoder and of the Llama decoder at equal layer sizes (random weights)."""
+    if args.design == "povusun":
+        return povusun_arm(args)
     import gc
     import torch
     from stratakv_b200.config import LlamaConfig, ZepavikConfig
@@ -513,7 +596,7 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
     parser.add_argument("--context", type=int, default=CONTEXT, help="context at which the timed decode steps end")
-    parser.add_argument("--design", choices=["zepavik"],
+    parser.add_argument("--design", choices=["zepavik", "povusun"],
                         help="measure this design beside the Llama decoder at equal layer sizes instead of the step benchmark")
     parser.add_argument("--sizes", default="", help="with --design: names of DESIGN_SIZES, with commas (default: all)")
     parser.add_argument("--window", type=int, default=0, help="with --design: the design's window (default: the whole context)")

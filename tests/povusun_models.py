@@ -48,7 +48,7 @@ def config(vocab, width, layers, side=None, eps=1e-5):
 #     values wider than keys, a latent wider than a head, a layer without a feed-forward, and a last layer that borrows
 #     the keys of layer 1 across two others; temperature periods of 7 and 5 tokens, a cap of 6.
 PA = config(97, 64, [rglru(48, 3, 3, mlp(40, 0.5)),
-                     attention(4, 1, 16, 24, 0.7, mlp(96, 2.0), softcap=6.0, q_temp=(0.5, 7)),
+                     attention(4, 1, 16, 24, 0.45, mlp(96, 2.0), softcap=6.0, q_temp=(0.5, 7)),
                      latent(3, 16, 8, 40, 0.3, None),
                      attention(4, 1, 16, 24, 0.5, mlp(56, 1.5), q_temp=(0.25, 5), kv_from=1)], side=8)
 # PB: sizes that are multiples of nothing much, no per-layer token input, attention without cap and temperature, a
@@ -58,10 +58,10 @@ PB = config(211, 72, [attention(6, 3, 20, 12, 0.6, mlp(100, 0.75)), latent(2, 24
                       attention(6, 3, 20, 12, 0.3, None, softcap=8.0, kv_from=0)], eps=1e-6)
 # PC: head size 64 for keys and values and a latent of 64 and of 128 (the sizes that kernels of one head size serve in
 #     bfloat16), a recurrent layer wider than the model with five taps.
-PC = config(300, 128, [attention(4, 2, 64, 64, 0.35, mlp(136, 1.0), softcap=10.0, q_temp=(0.3, 48)),
-                       latent(4, 32, 32, 64, 0.2, mlp(64, 2.0)), rglru(192, 2, 5, mlp(72, 1.0)),
-                       latent(2, 64, 48, 128, 0.15, None),
-                       attention(4, 2, 64, 64, 0.3, mlp(80, 0.5), softcap=10.0, kv_from=0)], side=4)
+PC = config(300, 128, [attention(4, 2, 64, 64, 0.25, mlp(136, 1.0), softcap=10.0, q_temp=(0.3, 48)),
+                       latent(4, 32, 32, 64, 0.15, mlp(64, 2.0)), rglru(192, 2, 5, mlp(72, 1.0)),
+                       latent(2, 64, 48, 128, 0.1, None),
+                       attention(4, 2, 64, 64, 0.2, mlp(80, 0.5), softcap=10.0, kv_from=0)], side=6)
 POVUSUN = {"PA": PA, "PB": PB, "PC": PC}
 
 
@@ -83,9 +83,14 @@ def make_folder(folder, raw_config, seed, dtype=torch.float32):
         elif name.endswith((".b",)) or name.endswith(".mix.conv"):
             tensors[name] = tensors[name] * 10.0
         elif kind == "latent_attention" and name.endswith((".mix.q", ".mix.uk")):
-            tensors[name] = tensors[name] * sharpen              # (no norm on these queries and keys)
-        elif name.endswith((".mix.ra", ".mix.ri", ".side.gate", ".side.proj", ".mix.g")):
+            # (no norm on these queries and keys: scores with a standard deviation of 2 to 3)
+            tensors[name] = tensors[name] * (sharpen if name.endswith(".mix.q") else sharpen ** 0.5)
+        elif name.endswith(".mix.dkv.norm"):
+            tensors[name] = 1.0 + (tensors[name] - 1.0) * 8.0     # a latent norm's weight that is far from all ones
+        elif name.endswith((".mix.ra", ".mix.ri", ".mix.g")):
             tensors[name] = tensors[name] * 5.0
+        # (the side input's gate stays small: where gelu_tanh of all of a token's few gate values is nearly zero, the
+        # norm after the projection blows up what is left of them, rounding included, in any implementation)
         elif name == "side.embed":
             tensors[name] = tensors[name] * 20.0
     folder = Path(folder)

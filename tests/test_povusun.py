@@ -127,7 +127,7 @@ def test_the_plain_implementation_tells_faults_from_rounding(tmp_path):
     config, weights = plain_povusun.load_folder(folder)
     tokens = random_tokens(POVUSUN[name]["vocab"], 90, seed=2)
     right = plain_povusun.logits_of(config, weights, tokens).numpy()
-    allowed = 0.06 * right.std()             # what tests/test_povusun_gpu.py allows a position in bfloat16
+    allowed = 0.08 * right.std()             # what tests/test_povusun_gpu.py allows a position in bfloat16
 
     def moved(change):
         other_config, other_weights = copy.deepcopy(config), dict(weights)
@@ -149,7 +149,7 @@ def test_the_plain_implementation_tells_faults_from_rounding(tmp_path):
     def no_second_norm(c, w): w["l1.norm1b"] = w["l1.norm1b"] * 2.0
     for change in (no_cap, no_temperature, no_gate, own_keys_of_another_layer, no_latent_norm_weight,
                    faster_decay, shifted_taps, no_conv_bias, other_limit, no_side_input, side_of_another_layer, no_second_norm):
-        assert moved(change) > 2 * allowed, change.__name__
+        assert moved(change) > 2 * allowed, f"{change.__name__}: {moved(change) / right.std():.3f} of the spread"
 
 
 def test_mechanisms_of_the_plain_implementation():

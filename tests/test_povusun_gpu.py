@@ -17,9 +17,9 @@ DTYPES = ["float32", "bfloat16"]
 # A position's logits may differ from the plain ones by this fraction of the logits' spread in the root mean square
 # over the vocabulary, and a single logit by four times that.  The test models' attention is peaked and their
 # recurrent layers remember long, so that bfloat16 rounding moves a position by a few hundredths of the spread while
-# a lost cap, gate, state or side input moves one by 0.12 or more (tests/test_povusun.py shows that on the plain
+# a lost cap, gate, state or side input moves one by 0.16 or more (tests/test_povusun.py shows that on the plain
 # implementation).  float32 differs by the order of its sums.
-ROW_NOISE = {"bfloat16": 0.06, "float32": 5e-5}
+ROW_NOISE = {"bfloat16": 0.08, "float32": 1.5e-4}
 
 
 class Folders:

@@ -225,9 +225,9 @@ def test_recurrent_unit_over_portions_batches_and_used_slots(dtype, shape):
 
     step([("a", 2, 5), ("b", 0, 1)])
     step([("b", 0, 1), ("a", 2, 1)])
-    step([("a", 2, 1), ("b", 0, 2)], twice=True)
+    step([("a", 2, 1), ("b", 0, 1)], twice=True)
     step([("a", 2, 1)], twice=True)
-    step([("a", 2, 2), ("b", 0, 5)])
+    step([("a", 2, 2), ("b", 0, 6)])
     step([("a", 2, 13)])
     step([("c", 0, 1)], twice=True)                 # slot 0 again: its new user starts from nothing
     step([("c", 0, 11)])
