@@ -167,7 +167,7 @@ DESIGN_SIZES = {
 def povusun_config(size, layers, vocab, kinds):
     """A Povusun configuration at a size of DESIGN_SIZES whose layer i has the mixer ``kinds[i % len(kinds)]``: the
     attention layers with Llama's heads (keys and values of one width, a cap, a temperature), the latent ones with a
-    latent of four heads' width (at most 512), the recurrent ones as wide as the model with a part per query head and
+    latent of four heads' width (at most 256, the widest head a kernel library is built for), the recurrent ones as wide as the model with a part per query head and
     four taps; every layer with a feed-forward of Llama's inner width (three matrices, as there) and a token input."""
     from stratakv_b200.config import PovusunConfig
     d, made, lender = size["head_dim"], [], None
@@ -181,7 +181,7 @@ def povusun_config(size, layers, vocab, kinds):
             elif lender is None:
                 lender = i
         elif kind == "latent_attention":
-            mixer = {"heads": size["heads"], "dim": d, "vdim": d, "kv_rank": min(512, 4 * d), "scale": d ** -0.5}
+            mixer = {"heads": size["heads"], "dim": d, "vdim": d, "kv_rank": min(256, 4 * d), "scale": d ** -0.5}
         else:
             mixer = {"width": size["hidden"], "blocks": size["heads"], "conv": 4}
         made.append({"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": size["llama_ff"], "limit": 7.0}})

@@ -80,6 +80,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int my_end = min(end_group, my_first + per_split);
     const int* table = block_table + (size_t)seq * table_width;
     const float scale_log2 = scale * 1.4426950408889634f;
+    const float cap_log2 = extras.softcap * 1.4426950408889634f;
+    const float inverse_cap_log2 = extras.softcap > 0.0f ? 1.0f / cap_log2 : 0.0f;
 
     // Q fragments: rows g and g+8 are heads head0+g and head0+g+8; 4 head-dim elements per k16 step
     uint32_t qa[KSTEPS][4];
@@ -141,6 +143,9 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                 float v = (key < ctx && key >= lo) ? s[t][c] * scale_log2 : -INFINITY;
                 if (extras.bias && key < ctx && key >= lo && g + 8 * (c >> 1) < rows)
                     v -= __ldg(extras.bias + (size_t)(head0 + g + 8 * (c >> 1)) * extras.bias_len + min(ctx - 1 - key, extras.bias_len - 1));
+                // (capped: the score in natural units is v / log2 e; a masked one stays -infinity)
+                if (extras.softcap > 0.0f && v != -INFINITY)
+                    v = cap_log2 * tanh_by_exp2(v * inverse_cap_log2);
                 s[t][c] = v;
                 tile_max[c >> 1] = fmaxf(tile_max[c >> 1], v);
             }
@@ -220,7 +225,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         }
         const int head = head0 + r;
         if (splits == 1) {
-            out[((size_t)seq * num_heads + head) * DHD + d] = __float2bfloat16_rn(total / sum * gate_factor(extras, seq, head));
+            out[((size_t)seq * num_heads + head) * DHD + d] =
+                __float2bfloat16_rn(total / sum * gate_factor(extras, seq, head) * gate_element(extras, seq, head, DHD, d));
         } else {
             const size_t at = ((size_t)seq * num_heads + head) * splits + split;
             partial_o[at * DHD + d] = total;
@@ -249,7 +255,8 @@ __global__ void decode_combine_kernel(const float* __restrict__ partial_o, const
             total += weight * partial_o[at * DHD + d];
             sum += weight * partial_ml[2 * at + 1];
         }
-        out[item * DHD + d] = __float2bfloat16_rn(total / sum * gated);
+        out[item * DHD + d] = __float2bfloat16_rn(total / sum * gated *
+                                                  gate_element(extras, item / num_heads, (int)(item % num_heads), DHD, d));
     }
 }
 
@@ -265,11 +272,12 @@ SKV_EXPORT int skv_attention_decode_extras(const void* q, const void* k_cache, c
                                            float* partial_o, float* partial_ml, int n_seqs, int num_heads,
                                            int num_kv_heads, int head_dim, int block_size, float scale, int window,
                                            int splits, const float* bias, int bias_len, const float* gate,
-                                           int gate_stride, cudaStream_t stream) {
+                                           int gate_stride, float softcap, int gate_per_element, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
-    if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads))
-        return fail("skv_attention_decode", "a bias table needs its length and a gate rows of at least heads numbers");
-    const AttentionExtras extras = {bias, bias_len, gate, gate_stride};
+    if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads * (gate_per_element ? head_dim : 1)) ||
+        (gate_per_element && !gate) || softcap < 0.0f)
+        return fail("skv_attention_decode", "a bias table needs its length, a gate rows of at least heads numbers (heads * head_dim with a gate per number), a cap must not be negative");
+    const AttentionExtras extras = {bias, bias_len, gate, gate_stride, softcap, gate_per_element};
     if (head_dim != DHD) return fail("skv_attention_decode", "this library was built for another head size");
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_decode", "heads must be a positive multiple of kv heads");
@@ -311,7 +319,7 @@ SKV_EXPORT int skv_attention_decode(const void* q, const void* k_cache, const vo
                                     int splits, cudaStream_t stream) {
     return skv_attention_decode_extras(q, k_cache, v_cache, block_table, table_width, ctx_after, out, partial_o,
                                        partial_ml, n_seqs, num_heads, num_kv_heads, head_dim, block_size, scale, window,
-                                       splits, nullptr, 0, nullptr, 0, stream);
+                                       splits, nullptr, 0, nullptr, 0, 0.0f, 0, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -412,7 +420,7 @@ SKV_EXPORT int skv_attention_decode(const void*, const void*, const void*, const
 
 SKV_EXPORT int skv_attention_decode_extras(const void*, const void*, const void*, const int*, int, const int*, void*,
                                            float*, float*, int, int, int, int, int, float, int, int, const float*, int,
-                                           const float*, int, cudaStream_t) {
+                                           const float*, int, float, int, cudaStream_t) {
     return skv::fail("skv_attention_decode", "the float32 build has no split decode kernel: use skv_attention");
 }
 

@@ -153,6 +153,25 @@ qkv_finish_kernel(const float* __restrict__ qkv, int row_stride, const float* __
         out[d] = from_float<T>((x[d] + (bias ? bias[d] : 0.0f)) * factor * (weight ? weight[d] : 1.0f));
 }
 
+// Rows of a paged cache with one head, copied into a plain matrix: out[i, :] = the row of position positions[i] of
+// sequence seqs[i] (for a mixer that needs its sequences' cached vectors side by side, as a GEMM's input).
+template <typename T>
+__global__ void __launch_bounds__(256)
+paged_gather_kernel(const T* __restrict__ cache, const int* __restrict__ block_table, int table_width,
+                    const int* __restrict__ positions, const int* __restrict__ seqs, T* __restrict__ out, int n_rows,
+                    int width, int block_size) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long i = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (i >= n_rows) return;
+    const int pos = positions[i];
+    const int block = block_table[(size_t)seqs[i] * table_width + pos / block_size];
+    const T* from = cache + ((size_t)block * block_size + pos % block_size) * width;
+    T* to = out + (size_t)i * width;
+    for (int d = lane; d < width; d += 32) to[d] = from[d];
+}
+
 __device__ __forceinline__ float general_dot(const float* __restrict__ q, const float* __restrict__ row, int dim) {
     float sum = 0.0f;
     if ((dim & 3) == 0) {
@@ -280,7 +299,7 @@ SKV_EXPORT int skv_qkv_finish(const float* qkv, int row_stride, const float* q_b
                               const float* k_weight, float q_temp_coef, int q_temp_every, int key_dim,
                               cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (num_heads <= 0 || num_kv_heads <= 0 || dim <= 0 || vdim < 0 || block_size <= 0)
+    if (num_heads < 0 || num_kv_heads <= 0 || dim <= 0 || vdim < 0 || block_size <= 0 || (num_heads > 0 && !q_out))
         return fail("skv_qkv_finish", "head counts, head sizes and block_size must be positive");
     if (key_dim <= 0) key_dim = dim;
     if (row_stride < (write_kv ? num_heads * dim + num_kv_heads * (key_dim + vdim) : num_heads * dim))
@@ -299,6 +318,15 @@ SKV_EXPORT int skv_qkv_finish(const float* qkv, int row_stride, const float* q_b
                       row_stride, q_bias, k_bias, v_bias, positions, token_seq, block_table, table_width,
                       (skv_t*)q_out, (skv_t*)k_cache, (skv_t*)v_cache, n_tokens, num_heads, num_kv_heads, dim, vdim,
                       block_size, value_norm, value_eps, write_kv, extras);
+}
+
+// cache: [blocks][1][block_size][width] in the compute dtype; out [n_rows, width].
+SKV_EXPORT int skv_paged_gather(const void* cache, const int* block_table, int table_width, const int* positions,
+                                const int* seqs, void* out, int n_rows, int width, int block_size, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width <= 0 || block_size <= 0 || table_width <= 0) return fail("skv_paged_gather", "sizes must be positive");
+    return launch_pdl("skv_paged_gather", paged_gather_kernel<skv_t>, dim3((n_rows + 7) / 8), dim3(256), 0, stream,
+                      (const skv_t*)cache, block_table, table_width, positions, seqs, (skv_t*)out, n_rows, width, block_size);
 }
 
 // `r1`, `r2`: float [num_heads] or both null.  `gate`: float, the gate's logit of (token t, head h) at

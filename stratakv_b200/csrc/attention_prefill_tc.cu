@@ -312,7 +312,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // with a bias by distance the scores are brought to units of log2 when the bias is taken off them,
         // and what follows multiplies by one
         const float* bias_row = EXTRAS && extras.bias ? extras.bias + (size_t)head * extras.bias_len : nullptr;
-        const float unit = EXTRAS && bias_row ? 1.0f : scale_log2;
+        const bool capped = EXTRAS && extras.softcap > 0.0f;
+        const float unit = EXTRAS && (bias_row || capped) ? 1.0f : scale_log2;
+        const float cap_log2 = capped ? extras.softcap * 1.4426950408889634f : 0.0f;
+        const float to_cap = capped ? scale / extras.softcap : 0.0f;
         float used_max = -INFINITY, row_sum = 0.0f;                   // in units of log2, after the scale
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
@@ -357,6 +360,14 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         sc[e] = fmaf(sc[e], scale_log2, -__ldg(bias_row + distance));
                     }
                 }
+            }
+            if (capped) {
+                // c * tanh(score / c), left in units of log2; with a bias the scores are in those units already.  A masked
+                // score must stay -infinity (its tanh would be -1).
+                const float into = bias_row ? 1.0f / cap_log2 : to_cap;
+#pragma unroll
+                for (int e = 0; e < ABN; ++e)
+                    sc[e] = sc[e] == -INFINITY ? -INFINITY : cap_log2 * tanh_by_exp2(sc[e] * into);
             }
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -421,11 +432,23 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inverse = (EXTRAS ? gate_factor(extras, q_begin + min(q_row, q_len - 1), head) : 1.0f) / row_sum;
             __nv_bfloat16* dst = out + ((size_t)(q_begin + min(q_row, q_len - 1)) * num_heads + head) * AHD;
+            const float* gate_row = EXTRAS && extras.gate && extras.gate_per_element
+                ? extras.gate + (size_t)(q_begin + min(q_row, q_len - 1)) * extras.gate_stride + (size_t)head * AHD : nullptr;
 #pragma unroll 1
             for (int c = 0; c < AHD; c += 32) {
                 uint32_t v[32];
                 a_ld32(tmem_o + lane_bits + (uint32_t)c, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (EXTRAS && gate_row) {                              // a gate for every number of the output
+#pragma unroll
+                    for (int d = 0; d < 32; d += 4) {
+                        const float4 logit = *(const float4*)(gate_row + c + d);
+                        v[d] = __float_as_uint(__fdividef(__uint_as_float(v[d]), 1.0f + __expf(-logit.x)));
+                        v[d + 1] = __float_as_uint(__fdividef(__uint_as_float(v[d + 1]), 1.0f + __expf(-logit.y)));
+                        v[d + 2] = __float_as_uint(__fdividef(__uint_as_float(v[d + 2]), 1.0f + __expf(-logit.z)));
+                        v[d + 3] = __float_as_uint(__fdividef(__uint_as_float(v[d + 3]), 1.0f + __expf(-logit.w)));
+                    }
+                }
                 if (q_row < q_len) {
 #pragma unroll
                     for (int d = 0; d < 32; d += 8) {
@@ -507,11 +530,13 @@ SKV_EXPORT int skv_attention_prefill_tc_extras(const void* q, const void* k_cach
                                                const int* ctx_after, void* out, int n_seqs, int n_tokens, int max_q_len,
                                                int num_heads, int num_kv_heads, int head_dim, int block_size, float scale,
                                                int window, const float* bias, int bias_len, const float* gate,
-                                               int gate_stride, int* flag, cudaStream_t stream) {
+                                               int gate_stride, float softcap, int gate_per_element, int* flag,
+                                               cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
-    if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads))
-        return fail("skv_attention_prefill_tc", "a bias table needs its length and a gate rows of at least heads numbers");
-    const AttentionExtras extras = {bias, bias_len, gate, gate_stride};
+    if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads * (gate_per_element ? head_dim : 1)) ||
+        (gate_per_element && (!gate || gate_stride % 4 != 0 || ((uintptr_t)gate & 15))) || softcap < 0.0f)
+        return fail("skv_attention_prefill_tc", "a bias table needs its length, a gate rows of at least heads numbers (with a gate per number: heads * head_dim, 16-byte aligned rows), a cap must not be negative");
+    const AttentionExtras extras = {bias, bias_len, gate, gate_stride, softcap, gate_per_element};
     if (head_dim != AHD) return fail("skv_attention_prefill_tc", "this library was built for another head size");
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_prefill_tc", "heads must be a positive multiple of kv heads");
@@ -537,7 +562,7 @@ SKV_EXPORT int skv_attention_prefill_tc_extras(const void* q, const void* k_cach
         }
         configured = true;
     }
-    return launch_pdl("skv_attention_prefill_tc", bias || gate ? prefill_attention_tc_kernel<true> : prefill_attention_tc_kernel<false>,
+    return launch_pdl("skv_attention_prefill_tc", bias || gate || softcap > 0.0f ? prefill_attention_tc_kernel<true> : prefill_attention_tc_kernel<false>,
                       dim3(num_heads, (unsigned)blocks),
                       dim3(ATHREADS), smem, stream, map_q, map_k, map_v, block_table, table_width, cu_q, ctx_after,
                       (__nv_bfloat16*)out, num_heads, num_kv_heads, block_size, rows_per_load, scale, window,
@@ -551,7 +576,7 @@ SKV_EXPORT int skv_attention_prefill_tc(const void* q, const void* k_cache, cons
                                         int window, int* flag, cudaStream_t stream) {
     return skv_attention_prefill_tc_extras(q, k_cache, v_cache, cache_blocks, block_table, table_width, cu_q, ctx_after,
                                            out, n_seqs, n_tokens, max_q_len, num_heads, num_kv_heads, head_dim, block_size,
-                                           scale, window, nullptr, 0, nullptr, 0, flag, stream);
+                                           scale, window, nullptr, 0, nullptr, 0, 0.0f, 0, flag, stream);
 }
 
 SKV_EXPORT int skv_has_attention_prefill_tc() { return 1; }
@@ -566,7 +591,7 @@ SKV_EXPORT int skv_attention_prefill_tc(const void*, const void*, const void*, i
 
 SKV_EXPORT int skv_attention_prefill_tc_extras(const void*, const void*, const void*, int, const int*, int, const int*,
                                                const int*, void*, int, int, int, int, int, int, int, float, int,
-                                               const float*, int, const float*, int, int*, cudaStream_t) {
+                                               const float*, int, const float*, int, float, int, int*, cudaStream_t) {
     return skv::fail("skv_attention_prefill_tc", "this build (float32, or a head size other than 64 or 128) has no such kernel");
 }
 

@@ -154,16 +154,36 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
 //          natural bias times log2 e: the kernels that take a table keep their scores so (2^x by the special-function
 //          unit).
 //   gate:  the logit of (token t, head h) at gate[t * gate_stride + h]; the head's output is multiplied by its sigmoid.
+//          With gate_per_element there is a logit for every number of the output, that of (token t, head h, number d)
+//          at gate[t * gate_stride + h * head_dim + d].
+//   softcap: c > 0 turns a score s into c * tanh(s / c) before the softmax (kernels that know it say so).
 struct AttentionExtras {
     const float* bias;
     int bias_len;
     const float* gate;
     int gate_stride;
+    float softcap;
+    int gate_per_element;
 };
 
+// tanh(x) = 1 - 2 / (1 + e^(2x)) with the special-function unit's exponential and reciprocal: an absolute error of a
+// few 1e-7, which is what a capped score needs (tanh.approx's 2^-11 relative error would be 0.01 on a cap of 30).
+__device__ __forceinline__ float tanh_by_exp2(float x) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return fmaf(-2.0f, r, 1.0f);
+}
+
 __device__ __forceinline__ float gate_factor(const AttentionExtras& extras, size_t token, int head) {
-    if (!extras.gate) return 1.0f;
+    if (!extras.gate || extras.gate_per_element) return 1.0f;
     return 1.0f / (1.0f + expf(-extras.gate[token * extras.gate_stride + head]));
+}
+
+// The factor of one output number where the gate is per number (1 otherwise).
+__device__ __forceinline__ float gate_element(const AttentionExtras& extras, size_t token, int head, int head_dim, int d) {
+    if (!extras.gate || !extras.gate_per_element) return 1.0f;
+    return 1.0f / (1.0f + expf(-extras.gate[token * extras.gate_stride + (size_t)head * head_dim + d]));
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -83,23 +83,56 @@ rglru_gates_kernel(float* __restrict__ gates, const float* __restrict__ u, float
     *y = gelu_tanh(*y + y_bias[c]);
 }
 
-// The recurrence itself: one thread per (sequence, channel) walks the sequence's tokens of this step.
+// The recurrence.  A sequence's tokens of this step are cut into chunks of `chunk` tokens and a thread walks one
+// chunk of one channel.  With more than one chunk a first pass (rglru_chunk_kernel) leaves for every chunk the product
+// A of its decays and the state B that it reaches from zero; the chunk's true first state then follows from the state
+// before the step and the (A, B) of the chunks in front: S <- A S + B, chunk by chunk.  So a prompt of thousands of
+// tokens is tens of short walks side by side and not one long one.  `summary` is [seqs][max_chunks][2][C] floats.
+__global__ void __launch_bounds__(128)
+rglru_chunk_kernel(const float* __restrict__ gates, float* __restrict__ summary, int n_seqs, int channels, int part,
+                   int chunk, int max_chunks, const int* __restrict__ cu_q) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y, k = blockIdx.z;
+    if (c >= channels || s >= n_seqs) return;
+    const int first = cu_q[s] + k * chunk, last = min(cu_q[s + 1] - 1, first + chunk - 1);
+    if (first > last) return;
+    const int b = c / part, within = c - b * part;
+    const float* pair = gates + (size_t)b * 2 * part + within;
+    float A = 1.0f, B = 0.0f;
+#pragma unroll 4
+    for (int t = first; t <= last; ++t) {
+        const float a = pair[(size_t)t * 2 * channels], driven = pair[(size_t)t * 2 * channels + part];
+        A *= a;
+        B = fmaf(a, B, driven);
+    }
+    float* mine = summary + ((size_t)s * max_chunks + k) * 2 * channels;
+    mine[c] = A;
+    mine[channels + c] = B;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 rglru_scan_kernel(const float* __restrict__ gates, const float* __restrict__ yx, int row_stride, int x_offset,
                   const float* __restrict__ x_bias, T* __restrict__ out, int out_stride, int n_seqs, int channels,
-                  int part, int taps, const RecurrentBatch batch) {
+                  int part, int taps, int chunk, int max_chunks, const float* __restrict__ summary,
+                  const RecurrentBatch batch) {
     pdl_launch_dependents();
     pdl_wait();
-    const int c = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y, k = blockIdx.z;
     if (c >= channels || s >= n_seqs) return;
-    const int first = batch.cu_q[s], last = batch.cu_q[s + 1] - 1;
-    if (last < first) return;
-    const int p_first = batch.positions[first], p_last = p_first + (last - first);
+    const int seq_first = batch.cu_q[s], seq_last = batch.cu_q[s + 1] - 1;
+    const int first = seq_first + k * chunk, last = min(seq_last, first + chunk - 1);
+    if (first > last) return;
+    const int p_first = batch.positions[seq_first], p_last = p_first + (seq_last - seq_first);
     float* state = batch.state + (size_t)batch.slot_ids[s] * batch.state_stride;
     const int b = c / part, within = c - b * part;
     const float* pair = gates + (size_t)b * 2 * part + within;
     float S = p_first > 0 ? state[(size_t)((p_first - 1) & 1) * channels + c] : 0.0f;
+    for (int j = 0; j < k; ++j) {                      // through the chunks in front of this one
+        const float* theirs = summary + ((size_t)s * max_chunks + j) * 2 * channels;
+        S = fmaf(theirs[c], S, theirs[channels + c]);
+    }
 #pragma unroll 4
     for (int t = first; t <= last; ++t) {
         const float a = pair[(size_t)t * 2 * channels], driven = pair[(size_t)t * 2 * channels + part];
@@ -107,11 +140,12 @@ rglru_scan_kernel(const float* __restrict__ gates, const float* __restrict__ yx,
         S = fmaf(a, S, driven);
         out[(size_t)t * out_stride + c] = from_float<T>(S * y);
     }
+    if (last != seq_last) return;                      // the sequence's last chunk leaves the state
     state[(size_t)(p_last & 1) * channels + c] = S;
     float* ring = state + 2 * (size_t)channels;
     const float bias = x_bias[c];
-    for (int back = 0; back < taps && last - back >= first; ++back)
-        ring[(size_t)((p_last - back) % taps) * channels + c] = yx[(size_t)(last - back) * row_stride + x_offset + c] + bias;
+    for (int back = 0; back < taps && seq_last - back >= seq_first; ++back)
+        ring[(size_t)((p_last - back) % taps) * channels + c] = yx[(size_t)(seq_last - back) * row_stride + x_offset + c] + bias;
 }
 
 }  // namespace skv
@@ -152,9 +186,19 @@ SKV_EXPORT int skv_rglru_gates(float* gates, const float* u, float* yx, int row_
                       row_stride, y_bias, r_bias, i_bias, lam, n_tokens, channels, part);
 }
 
+constexpr int RGLRU_CHUNK = 64;
+
+// Floats of `summary` that a step whose longest sequence brings max_q_len tokens needs (0: none, it runs as one chunk).
+SKV_EXPORT long long skv_rglru_scan_scratch(int n_seqs, int max_q_len, int channels) {
+    if (max_q_len <= 2 * RGLRU_CHUNK) return 0;
+    return (long long)n_seqs * ((max_q_len + RGLRU_CHUNK - 1) / RGLRU_CHUNK) * 2 * channels;
+}
+
 // out [tokens, out_stride] in the compute dtype: S * activated gate branch, the input of the output projection.
+// max_q_len: the most tokens a sequence brings; summary: skv_rglru_scan_scratch floats (null where that is 0).
 SKV_EXPORT int skv_rglru_scan(const float* gates, const float* yx, int row_stride, int x_offset, const float* x_bias,
-                              void* out, int out_stride, int n_seqs, int channels, int part, int taps,
+                              void* out, int out_stride, int n_seqs, int channels, int part, int taps, int max_q_len,
+                              float* summary,
                               const int* positions, const int* token_seq, const int* cu_q, const int* slot_ids,
                               float* state, int state_stride, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
@@ -163,7 +207,18 @@ SKV_EXPORT int skv_rglru_scan(const float* gates, const float* yx, int row_strid
     if (n_seqs > 65535) return fail("skv_rglru_scan", "too many sequences in one step");
     if (out_stride < channels) return fail("skv_rglru_scan", "a row of the output is shorter than its channels");
     const RecurrentBatch batch = {positions, token_seq, cu_q, slot_ids, state, state_stride};
-    return launch_pdl("skv_rglru_scan", rglru_scan_kernel<skv_t>, dim3((channels + 127) / 128, n_seqs), dim3(128), 0,
+    if (max_q_len <= 0) return fail("skv_rglru_scan", "the longest sequence's token count is needed");
+    const bool chunked = skv_rglru_scan_scratch(n_seqs, max_q_len, channels) > 0;
+    if (chunked && !summary) return fail("skv_rglru_scan", "a step this long needs scratch for its chunks");
+    const int chunk = chunked ? RGLRU_CHUNK : max_q_len;
+    const int max_chunks = (max_q_len + chunk - 1) / chunk;
+    if (max_chunks > 65535) return fail("skv_rglru_scan", "too many tokens of one sequence in one step");
+    const dim3 grid((channels + 127) / 128, n_seqs, max_chunks);
+    if (chunked)
+        if (int code = launch_pdl("skv_rglru_scan", rglru_chunk_kernel, grid, dim3(128), 0, stream, gates, summary, n_seqs,
+                                  channels, part, chunk, max_chunks, cu_q))
+            return code;
+    return launch_pdl("skv_rglru_scan", rglru_scan_kernel<skv_t>, grid, dim3(128), 0,
                       stream, gates, yx, row_stride, x_offset, x_bias, (skv_t*)out, out_stride, n_seqs, channels, part,
-                      taps, batch);
+                      taps, chunk, max_chunks, (const float*)summary, batch);
 }

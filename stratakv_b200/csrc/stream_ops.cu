@@ -41,51 +41,84 @@ __global__ void rmsnorm_add_kernel(const float* __restrict__ y, const float* __r
         out_row[c] = from_float<T>(x_row[c] * next_inverse * next_gamma[c]);
 }
 
+// A block takes SIDE_TOKENS tokens, so that it reads the two weights once for all of them: `proj_t` is the projection
+// transposed, [dim][hidden], which lets neighbouring threads read neighbouring columns.
+constexpr int SIDE_TOKENS = 4;
+
 template <typename T>
 __global__ void token_side_kernel(float* __restrict__ x, const int* __restrict__ ids, const T* __restrict__ table,
                                   int table_stride, int offset, int dim, int vocab, const T* __restrict__ gate_w,
-                                  const T* __restrict__ proj_w, const float* __restrict__ norm_w, float eps,
+                                  const T* __restrict__ proj_t, const float* __restrict__ norm_w, float eps,
                                   const float* __restrict__ next_gamma, float next_eps, T* __restrict__ next_out,
-                                  int hidden) {
-    extern __shared__ __align__(16) float side_shared[];       // [dim] gated values, [hidden] projected values
+                                  int n_tokens, int hidden) {
+    extern __shared__ __align__(16) float side_shared[];       // [tokens][dim] gated values, [tokens][hidden] projected
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
     float* gated = side_shared;
-    float* projected = side_shared + dim;
-    const size_t t = blockIdx.x;
-    float* x_row = x + t * hidden;
-    const int id = ids[t];
-    const bool known = id >= 0 && id < vocab;                  // (the embedding has flagged an id outside the table)
+    float* projected = side_shared + SIDE_TOKENS * dim;
+    const int t0 = blockIdx.x * SIDE_TOKENS;
+    const int count = min(SIDE_TOKENS, n_tokens - t0);
+    const float* rows[SIDE_TOKENS];
+#pragma unroll
+    for (int k = 0; k < SIDE_TOKENS; ++k) rows[k] = x + (size_t)(t0 + min(k, count - 1)) * hidden;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     for (int j = warp; j < dim; j += warps) {
         const T* w_row = gate_w + (size_t)j * hidden;
-        float dot = 0.0f;
-        for (int c = lane; c < hidden; c += 32) dot = fmaf(to_float(w_row[c]), x_row[c], dot);
-        dot = warp_sum(dot);
-        if (lane == 0) gated[j] = known ? gelu_tanh(dot) * to_float(table[(size_t)id * table_stride + offset + j]) : 0.0f;
+        float dot[SIDE_TOKENS] = {};
+        for (int c = lane; c < hidden; c += 32) {
+            const float w = to_float(w_row[c]);
+#pragma unroll
+            for (int k = 0; k < SIDE_TOKENS; ++k) dot[k] = fmaf(w, rows[k][c], dot[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < SIDE_TOKENS; ++k) {
+            const float total = warp_sum(dot[k]);
+            if (lane == 0) {
+                const int id = ids[t0 + min(k, count - 1)];
+                // (the embedding has flagged an id outside the table)
+                const bool known = id >= 0 && id < vocab;
+                gated[k * dim + j] = known ? gelu_tanh(total) * to_float(table[(size_t)id * table_stride + offset + j]) : 0.0f;
+            }
+        }
     }
     __syncthreads();
-    float partial = 0.0f;
+    float partial[SIDE_TOKENS] = {};
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const T* w_row = proj_w + (size_t)c * dim;
-        float sum = 0.0f;
-        for (int j = 0; j < dim; ++j) sum = fmaf(to_float(w_row[j]), gated[j], sum);
-        projected[c] = sum;
-        partial = fmaf(sum, sum, partial);
+        float sum[SIDE_TOKENS] = {};
+        for (int j = 0; j < dim; ++j) {
+            const float w = to_float(proj_t[(size_t)j * hidden + c]);
+#pragma unroll
+            for (int k = 0; k < SIDE_TOKENS; ++k) sum[k] = fmaf(w, gated[k * dim + j], sum[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < SIDE_TOKENS; ++k) {
+            projected[(size_t)k * hidden + c] = sum[k];
+            partial[k] = fmaf(sum[k], sum[k], partial[k]);
+        }
     }
-    const float inverse_rms = 1.0f / sqrtf(block_sum(partial, scratch) / (float)hidden + eps);
-    float squares = 0.0f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float v = x_row[c] + projected[c] * inverse_rms * norm_w[c];
-        x_row[c] = v;
-        squares = fmaf(v, v, squares);
+    float inverse_rms[SIDE_TOKENS];
+#pragma unroll
+    for (int k = 0; k < SIDE_TOKENS; ++k) inverse_rms[k] = 1.0f / sqrtf(block_sum(partial[k], scratch) / (float)hidden + eps);
+    float squares[SIDE_TOKENS] = {};
+    for (int k = 0; k < count; ++k) {
+        float* x_row = x + (size_t)(t0 + k) * hidden;
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float v = x_row[c] + projected[(size_t)k * hidden + c] * inverse_rms[k] * norm_w[c];
+            x_row[c] = v;
+            squares[k] = fmaf(v, v, squares[k]);
+        }
     }
     if (!next_out) return;
-    const float next_inverse = 1.0f / sqrtf(block_sum(squares, scratch) / (float)hidden + next_eps);
-    T* out_row = next_out + t * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
-        out_row[c] = from_float<T>(x_row[c] * next_inverse * next_gamma[c]);
+#pragma unroll
+    for (int k = 0; k < SIDE_TOKENS; ++k) {
+        const float next_inverse = 1.0f / sqrtf(block_sum(squares[k], scratch) / (float)hidden + next_eps);
+        if (k >= count) continue;
+        const float* x_row = x + (size_t)(t0 + k) * hidden;
+        T* out_row = next_out + (size_t)(t0 + k) * hidden;
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x)     // (each thread reads back what it wrote itself)
+            out_row[c] = from_float<T>(x_row[c] * next_inverse * next_gamma[c]);
+    }
 }
 
 }  // namespace skv
@@ -107,9 +140,9 @@ SKV_EXPORT int skv_rmsnorm_add(const float* y, const float* gamma, float eps, fl
 }
 
 // table [vocab, table_stride], of whose rows the columns offset .. offset + dim - 1 are this layer's; gate_w
-// [dim, hidden]; proj_w [hidden, dim]; norm_w float [hidden].
+// [dim, hidden]; proj_t [dim, hidden], the projection transposed; norm_w float [hidden].
 SKV_EXPORT int skv_token_side(float* x, const int* ids, const void* table, int table_stride, int offset, int dim,
-                              int vocab, const void* gate_w, const void* proj_w, const float* norm_w, float eps,
+                              int vocab, const void* gate_w, const void* proj_t, const float* norm_w, float eps,
                               const float* next_gamma, float next_eps, void* next_out, int n_tokens, int hidden,
                               cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
@@ -117,7 +150,7 @@ SKV_EXPORT int skv_token_side(float* x, const int* ids, const void* table, int t
     if (offset < 0 || offset + dim > table_stride) return fail("skv_token_side", "the layer's columns lie outside the table");
     if ((next_gamma == nullptr) != (next_out == nullptr))
         return fail("skv_token_side", "the next norm needs its weight and a place for its result");
-    const size_t smem = (size_t)(dim + hidden) * sizeof(float);
+    const size_t smem = (size_t)SIDE_TOKENS * (dim + hidden) * sizeof(float);
     if (smem > 200 * 1024) return fail("skv_token_side", "the stream is too wide for one block's shared memory");
     auto kernel = token_side_kernel<skv_t>;
     if (smem > 48 * 1024) {
@@ -128,7 +161,9 @@ SKV_EXPORT int skv_token_side(float* x, const int* ids, const void* table, int t
             raised = true;
         }
     }
-    return launch_pdl("skv_token_side", kernel, dim3(n_tokens), dim3(stream_threads(hidden)), smem, stream, x, ids,
-                      (const skv_t*)table, table_stride, offset, dim, vocab, (const skv_t*)gate_w, (const skv_t*)proj_w,
-                      norm_w, eps, next_gamma, next_eps, (skv_t*)next_out, hidden);
+    // few tokens: the blocks are few, so each is as large as it can be
+    const int threads = n_tokens <= 64 * SIDE_TOKENS ? 1024 : stream_threads(hidden);
+    return launch_pdl("skv_token_side", kernel, dim3((n_tokens + SIDE_TOKENS - 1) / SIDE_TOKENS), dim3(threads), smem,
+                      stream, x, ids, (const skv_t*)table, table_stride, offset, dim, vocab, (const skv_t*)gate_w,
+                      (const skv_t*)proj_t, norm_w, eps, next_gamma, next_eps, (skv_t*)next_out, n_tokens, hidden);
 }

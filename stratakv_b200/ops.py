@@ -295,16 +295,20 @@ class Kernels:
             _ptr(token_seq), _ptr(out), n, num_heads, num_kv_heads, head_dim, block_size,
             ctypes.c_float(scale), window, _stream()), "attention")
 
-    def _extras(self, bias, gate, gate_stride: int, num_heads: int, name: str):
-        """Arguments (bias table, its length, gate logits, their row stride) of the attention kernels' optional terms."""
+    def _extras(self, bias, gate, gate_stride: int, num_heads: int, name: str, per_element_width: int = 0):
+        """Arguments (bias table, its length, gate logits, their row stride) of the attention kernels' optional terms.
+        ``per_element_width``: the gate holds a logit for every output number, that many a head."""
         bias_len = 0
         if bias is not None:
             self._want(bias, torch.float32, "bias")
             if bias.dim() != 2 or bias.shape[0] != num_heads or bias.shape[1] < 1:
                 raise KernelError(f"{name}: the bias table must be [heads, distances]")
             bias_len = bias.shape[1]
-        if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda or gate_stride < num_heads):
+        if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda
+                                 or gate_stride < num_heads * max(1, per_element_width)):
             raise KernelError(f"{name}: the gate must be float32 on the GPU, a row at least heads wide")
+        if per_element_width and gate is None:
+            raise KernelError(f"{name}: a gate per output number needs the gate")
         return _ptr(bias), bias_len, _ptr(gate), int(gate_stride) if gate is not None else 0
 
     def has_attention_prefill(self) -> bool:
@@ -336,8 +340,11 @@ class Kernels:
 
     def attention_prefill_tc(self, q, k_cache, v_cache, block_table, cu_q, ctx_after, out, max_q_len: int,
                              num_heads: int, num_kv_heads: int, head_dim: int, block_size: int, scale: float,
-                             window: int = 0, flag=None, bias=None, gate=None, gate_stride: int = 0):
-        """``attention_prefill`` with both products on the tcgen05 tensor cores (bfloat16, head size 64 or 128)."""
+                             window: int = 0, flag=None, bias=None, gate=None, gate_stride: int = 0,
+                             softcap: float = 0.0, gate_per_element: bool = False):
+        """``attention_prefill`` with both products on the tcgen05 tensor cores (bfloat16, head size 64 or 128).
+        ``softcap`` c > 0: scores become ``c * tanh(score / c)``; ``gate_per_element``: a logit for every output
+        number, at ``[t * gate_stride + h * head_dim + d]``."""
         self._want(q, self.dtype, "q"); self._want(out, self.dtype, "out")
         self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
         self._want(block_table, torch.int32, "block_table"); self._want(cu_q, torch.int32, "cu_q")
@@ -351,13 +358,16 @@ class Kernels:
             _ptr(q), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table), block_table.shape[1],
             _ptr(cu_q), _ptr(ctx_after), _ptr(out), n_seqs, q.shape[0], max_q_len, num_heads, num_kv_heads, head_dim,
             block_size, ctypes.c_float(scale), window,
-            *self._extras(bias, gate, gate_stride, num_heads, "attention_prefill_tc"),
+            *self._extras(bias, gate, gate_stride, num_heads, "attention_prefill_tc", head_dim if gate_per_element else 0),
+            ctypes.c_float(softcap), int(bool(gate_per_element)),
             _ptr(flag if flag is not None else self.error_flag), _stream()), "attention_prefill_tc")
 
     def attention_decode(self, q, k_cache, v_cache, block_table, ctx_after, out, num_heads: int,
                          num_kv_heads: int, head_dim: int, block_size: int, scale: float, window: int = 0,
-                         splits: int = 1, scratch_o=None, scratch_ml=None, bias=None, gate=None, gate_stride: int = 0):
-        """(``bias``, ``gate``: as in ``attention_prefill``.)
+                         splits: int = 1, scratch_o=None, scratch_ml=None, bias=None, gate=None, gate_stride: int = 0,
+                         softcap: float = 0.0, gate_per_element: bool = False):
+        """(``bias``, ``gate``: as in ``attention_prefill``; ``softcap``, ``gate_per_element``: as in
+        ``attention_prefill_tc``.)
         One new token per sequence (bfloat16 build): ``ctx_after[s]`` keys are cached for sequence
         ``s``, the newest being the query's own.  ``splits`` > 1 cuts each context across blocks and
         needs float scratch: ``scratch_o`` [seqs*heads*splits*head_dim], ``scratch_ml`` [seqs*heads*splits*2]."""
@@ -374,8 +384,9 @@ class Kernels:
         self._check(self.lib.skv_attention_decode_extras(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(ctx_after),
             _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), n, num_heads, num_kv_heads, head_dim, block_size,
-            ctypes.c_float(scale), window, splits, *self._extras(bias, gate, gate_stride, num_heads, "attention_decode"),
-            _stream()), "attention_decode")
+            ctypes.c_float(scale), window, splits,
+            *self._extras(bias, gate, gate_stride, num_heads, "attention_decode", head_dim if gate_per_element else 0),
+            ctypes.c_float(softcap), int(bool(gate_per_element)), _stream()), "attention_decode")
 
     def has_attention_decode_fused(self) -> bool:
         return bool(self.lib.skv_has_attention_decode_fused())
@@ -467,7 +478,9 @@ class Kernels:
         None: the rows hold no values.  With ``write_kv`` false a row need hold its queries only.  ``key_dim``: the
         width of a key head where it is not a query head's (a compressed latent that is cached as the one key)."""
         key_dim = key_dim or dim
-        self._want(qkv, torch.float32, "qkv"); self._want(q_out, self.dtype, "q_out")
+        self._want(qkv, torch.float32, "qkv")
+        if num_heads > 0:
+            self._want(q_out, self.dtype, "q_out")
         self._want(positions, torch.int32, "positions"); self._want(token_seq, torch.int32, "token_seq")
         self._want(block_table, torch.int32, "block_table")
         self._want(k_cache, self.dtype, "k_cache")
@@ -480,7 +493,8 @@ class Kernels:
                 if bias.numel() != width:
                     raise KernelError(f"qkv_finish: {name} must hold {width} numbers")
         n = qkv.shape[0]
-        if tuple(q_out.shape) != (n, num_heads * dim) or positions.numel() != n or token_seq.numel() != n:
+        if ((num_heads > 0 and tuple(q_out.shape) != (n, num_heads * dim)) or positions.numel() != n
+                or token_seq.numel() != n):
             raise KernelError("qkv_finish: one query row, one position and one sequence index per token is needed")
         if (tuple(k_cache.shape[1:]) != (num_kv_heads, block_size, key_dim)
                 or (v_cache is not None and tuple(v_cache.shape[1:]) != (num_kv_heads, block_size, vdim))):
@@ -531,6 +545,18 @@ class Kernels:
             window, _ptr(r1), _ptr(r2), _ptr(gate), gate_stride, out.shape[1], ctypes.c_float(softcap),
             int(bool(gate_per_element)), _stream()), "attention_general")
 
+    def paged_gather(self, cache, block_table, positions, seqs, out):
+        """``out[i, :]`` = the row that a one-head paged cache (``[blocks, 1, block_size, width]``) holds for position
+        ``positions[i]`` of sequence ``seqs[i]`` (a row of ``block_table``)."""
+        self._want(cache, self.dtype, "cache"); self._want(out, self.dtype, "out")
+        self._want(block_table, torch.int32, "block_table"); self._want(positions, torch.int32, "positions")
+        self._want(seqs, torch.int32, "seqs")
+        n, width = out.shape
+        if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != width or positions.numel() != n or seqs.numel() != n:
+            raise KernelError("paged_gather: shapes do not agree")
+        self._check(self.lib.skv_paged_gather(_ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(positions),
+                                              _ptr(seqs), _ptr(out), n, width, cache.shape[2], _stream()), "paged_gather")
+
     def rmsnorm_add(self, y, gamma, eps: float, x, next_gamma=None, next_eps: float = 0.0, next_out=None):
         """x += rmsnorm(y) * gamma on float32 rows (the norm after a sublayer); with ``next_gamma`` and ``next_out``
         (compute dtype) also ``next_out = rmsnorm(new x) * next_gamma``, the input of the sublayer after it."""
@@ -545,16 +571,16 @@ class Kernels:
         self._check(self.lib.skv_rmsnorm_add(_ptr(y), _ptr(gamma), ctypes.c_float(eps), _ptr(x), _ptr(next_gamma),
                                              ctypes.c_float(next_eps), _ptr(next_out), n, hidden, _stream()), "rmsnorm_add")
 
-    def token_side(self, x, ids, table, offset: int, dim: int, gate_w, proj_w, norm_w, eps: float, next_gamma=None,
+    def token_side(self, x, ids, table, offset: int, dim: int, gate_w, proj_t, norm_w, eps: float, next_gamma=None,
                    next_eps: float = 0.0, next_out=None):
         """An input that depends on the token, added to the float32 stream: ``e = table[id, offset:offset + dim]``,
-        ``g = gelu_tanh(gate_w . x) * e``, ``y = proj_w . g``, ``x += rmsnorm(y) * norm_w``; ``next_*`` as in
-        ``rmsnorm_add``."""
+        ``g = gelu_tanh(gate_w . x) * e``, ``y = proj_t^T . g`` (``proj_t`` is the projection transposed,
+        ``[dim, hidden]``), ``x += rmsnorm(y) * norm_w``; ``next_*`` as in ``rmsnorm_add``."""
         self._want(x, torch.float32, "x"); self._want(ids, torch.int32, "ids"); self._want(table, self.dtype, "table")
-        self._want(gate_w, self.dtype, "gate_w"); self._want(proj_w, self.dtype, "proj_w")
+        self._want(gate_w, self.dtype, "gate_w"); self._want(proj_t, self.dtype, "proj_t")
         self._want(norm_w, torch.float32, "norm_w")
         n, hidden = x.shape
-        if (ids.numel() != n or tuple(gate_w.shape) != (dim, hidden) or tuple(proj_w.shape) != (hidden, dim)
+        if (ids.numel() != n or tuple(gate_w.shape) != (dim, hidden) or tuple(proj_t.shape) != (dim, hidden)
                 or norm_w.numel() != hidden or table.dim() != 2):
             raise KernelError("token_side: shapes do not agree")
         if next_out is not None:
@@ -563,7 +589,7 @@ class Kernels:
                 raise KernelError("token_side: the next norm's shapes do not agree")
         self._check(self.lib.skv_token_side(
             _ptr(x), _ptr(ids), _ptr(table), table.shape[1], int(offset), int(dim), table.shape[0], _ptr(gate_w),
-            _ptr(proj_w), _ptr(norm_w), ctypes.c_float(eps), _ptr(next_gamma), ctypes.c_float(next_eps), _ptr(next_out),
+            _ptr(proj_t), _ptr(norm_w), ctypes.c_float(eps), _ptr(next_gamma), ctypes.c_float(next_eps), _ptr(next_out),
             n, hidden, _stream()), "token_side")
 
     def headwise_linear(self, x, w, out, heads: int, zero_pad: bool = False):
@@ -624,19 +650,33 @@ class Kernels:
         self._check(self.lib.skv_rglru_gates(_ptr(gates), _ptr(u), _ptr(yx), yx.shape[1], _ptr(y_bias), _ptr(r_bias),
                                              _ptr(i_bias), _ptr(lam), n, channels, int(part), _stream()), "rglru_gates")
 
-    def rglru_scan(self, gates, yx, x_offset: int, x_bias, out, part: int, taps: int, step_meta, state):
+    def rglru_scan_scratch(self, n_seqs: int, max_q_len: int, channels: int) -> int:
+        """Floats of scratch ``rglru_scan`` needs for a step whose longest sequence brings ``max_q_len`` tokens."""
+        self.lib.skv_rglru_scan_scratch.restype = ctypes.c_longlong
+        return int(self.lib.skv_rglru_scan_scratch(int(n_seqs), int(max_q_len), int(channels)))
+
+    def rglru_scan(self, gates, yx, x_offset: int, x_bias, out, part: int, taps: int, step_meta, state,
+                   max_q_len: int, summary=None):
         """``S_t = a_t S_(t-1) + driven_t`` along each sequence's tokens of this step, from and to ``state``;
-        ``out[t, :C] = S_t * yx[t, :C]`` in the compute dtype; the convolution's last inputs go to ``state`` too."""
+        ``out[t, :C] = S_t * yx[t, :C]`` in the compute dtype; the convolution's last inputs go to ``state`` too.
+        ``max_q_len``: the most tokens one sequence brings; long steps are walked in chunks side by side and need
+        ``summary``, float32 scratch of ``rglru_scan_scratch`` numbers."""
         self._want(gates, torch.float32, "gates"); self._want(yx, torch.float32, "yx")
         self._want(out, self.dtype, "out"); self._want(x_bias, torch.float32, "x_bias")
         n, channels = gates.shape[0], gates.shape[1] // 2
         n_seqs = step_meta[3].numel()
         if yx.shape[0] != n or out.shape[0] != n or out.shape[1] < channels or x_bias.numel() != channels:
             raise KernelError("rglru_scan: shapes do not agree")
+        if summary is not None:
+            self._want(summary, torch.float32, "summary")
+            if summary.numel() < self.rglru_scan_scratch(n_seqs, max_q_len, channels):
+                raise KernelError("rglru_scan: the scratch for the chunks is too small")
         self._check(self.lib.skv_rglru_scan(
             _ptr(gates), _ptr(yx), yx.shape[1], int(x_offset), _ptr(x_bias), _ptr(out), out.shape[1], n_seqs, channels,
-            int(part), int(taps), *self._recurrent_batch(step_meta, state, channels, taps, "rglru_scan"), _stream()),
-            "rglru_scan")
+            int(part), int(taps), int(max_q_len), _ptr(summary),
+            *self._recurrent_batch(step_meta, state, channels, taps, "rglru_scan"), _stream()), "rglru_scan")
+        if summary is not None and self.rglru_scan_scratch(n_seqs, max_q_len, channels) > 0:
+            Kernels.launches += 1              # (the pass that sums up the chunks)
 
     def scale_inplace(self, x, factor: float):
         self._want(x, torch.float32, "x")

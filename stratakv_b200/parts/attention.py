@@ -174,8 +174,7 @@ class PagedAttention(Mixer):
         """True if the kernels that are compiled for one head size can serve this mixer: bfloat16, keys and values
         of one width that a library can be built for, and a distance bias (if any) that fits a table."""
         s = self.spec
-        return (not s.needs_general_kernels
-                and self.rt.dtype == torch.bfloat16 and s.value_dim == s.head_dim and s.head_dim % 16 == 0
+        return (self.rt.dtype == torch.bfloat16 and s.value_dim == s.head_dim and s.head_dim % 16 == 0
                 and s.head_dim <= 256 and self.rt.device.type == "cuda"
                 and (not s.distance_bias or s.window > 0 or s.distance_bias.max_distance > 0))
 
@@ -189,7 +188,9 @@ class PagedAttention(Mixer):
         ops.linear(h, self.w_qkv, fused, _ops.MODE_STORE_F32)
         k_cache, v_cache = step.cache.entry_kv(cache_entry)
         table = step.block_tables[step.cache.entry_group_index(cache_entry)]
-        if step.is_decode and self._specialised():
+        if step.is_decode and self._specialised() and not s.needs_general_kernels:
+            # (the kernel that finishes the new token itself knows biases and the value norm, not the unit norms,
+            # the temperature or rows without keys: those go through qkv_finish and the split kernel)
             ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
             if self._decode_fused(step, fused, ctx, k_cache, v_cache, table, writes_cache):
                 ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
@@ -240,7 +241,8 @@ class PagedAttention(Mixer):
         s, rt = self.spec, self.rt
         ops = rt.kernels(s.head_dim)
         n = q.shape[0]
-        extras = dict(bias=self.bias_table, gate=gate, gate_stride=self.fused_width)
+        extras = dict(bias=self.bias_table, gate=gate, gate_stride=self.fused_width, softcap=s.softcap,
+                      gate_per_element=s.gate_per_element)
         block_size = step.cache.block_size
         if step.is_decode:
             if block_size % 16 != 0:
@@ -260,7 +262,8 @@ class PagedAttention(Mixer):
             ops.attention_prefill_tc(q, k_cache, v_cache, table, step.cu_q, step.ctx_after, ctx, step.max_q_len,
                                      s.num_heads, s.num_kv_heads, s.head_dim, block_size, s.scale, s.window, **extras)
             return True
-        if ops.has_attention_prefill() and s.num_heads <= 65535:
+        if ops.has_attention_prefill() and s.num_heads <= 65535 and not s.softcap and not s.gate_per_element:
+            del extras["softcap"], extras["gate_per_element"]
             ops.attention_prefill(q, k_cache, v_cache, table, step.cu_q, step.ctx_after, ctx, step.max_q_len,
                                   s.num_heads, s.num_kv_heads, s.head_dim, block_size, s.scale, s.window, **extras)
             return True

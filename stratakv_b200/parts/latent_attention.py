@@ -6,9 +6,15 @@ Head h's keys and values are ``Wuk[h] c`` and ``Wuv[h] c``; they are never made.
 keys' up-projection into the queries (``headwise_linear`` with the transposed matrices), attends with every head over
 the same cached vectors as keys and as values (the attention kernels with one key/value head of ``latent_dim``), and
 applies the values' up-projection to each head's result.  No position encoding.
+
+That is how one token a sequence runs, and every step in float32.  A prompt in bfloat16 whose heads have a size the
+tensor-core prompt kernel is built for goes the other way round: the cached vectors of the step's sequences are
+gathered, up-projected by one GEMM into keys and values of all heads, laid out as pages of a scratch cache, and
+attended over as ordinary multi-head attention; the work per key is then ``head_dim`` and not ``latent_dim`` numbers.
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from .. import ops as _ops
@@ -62,6 +68,9 @@ class LatentAttention(Mixer):
         k_up = self.rt.upload(tensors[s.k_up_weight]).view(s.num_heads, s.head_dim, s.latent_dim)
         self.w_k_up_t = k_up.transpose(1, 2).contiguous()       # [heads, latent, head_dim]: q -> q in latent space
         self.w_v_up = self.rt.upload(tensors[s.v_up_weight]).view(s.num_heads, s.v_head_dim, s.latent_dim).contiguous()
+        # keys' and values' up-projections as one matrix, for steps that make every head's keys and values
+        self.w_kv_up = torch.cat([self.rt.upload(tensors[s.k_up_weight]), self.rt.upload(tensors[s.v_up_weight])],
+                                 dim=0).contiguous()
         w_o = self.rt.upload(tensors[s.o_weight])
         if self.ctx_width != self.ctx_dim:
             w_o = torch.cat([w_o, w_o.new_zeros(s.hidden_size, self.ctx_width - self.ctx_dim)], dim=1)
@@ -74,21 +83,99 @@ class LatentAttention(Mixer):
         fused = rt.workspace.get("qkv", (n, self.fused_width), torch.float32)
         ops.linear(h, self.w_q_down, fused, _ops.MODE_STORE_F32)
         latents = step.cache.entry_storage(cache_entry)["c"]
-        table = step.block_tables[step.cache.entry_group_index(cache_entry)]
+        group = step.cache.entry_group_index(cache_entry)
+        table = step.block_tables[group]
         block_size = step.cache.block_size
         q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
         # queries pass as they are; the one "key head" of a row is the latent, normed with its weight and cached
         ops.qkv_finish(fused, q, latents, None, step.positions, step.token_seq, table, s.num_heads, 1, s.head_dim, 0,
                        block_size, write_kv=writes_cache, k_norm=True, qk_norm_eps=s.eps,
                        k_norm_weight=self.latent_gamma, key_dim=s.latent_dim)
+        ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
+        if not self._attend_expanded(step, q, ctx, latents, table, group):
+            self._attend_folded(step, q, ctx, latents, table)
+        ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
+
+    def _attend_folded(self, step, q, ctx, latents, table):
+        """The up-projections folded into queries and outputs; attention of all heads over the cached vectors."""
+        s, rt = self.spec, self.rt
+        ops = rt.kernels()
+        n = q.shape[0]
+        block_size = step.cache.block_size
         q_latent = rt.workspace.get("q_latent", (n, s.num_heads * s.latent_dim), rt.dtype)
         ops.headwise_linear(q, self.w_k_up_t, q_latent, s.num_heads)
         mixed = rt.workspace.get("latent_ctx", (n, s.num_heads * s.latent_dim), rt.dtype)
-        ops.attention_general(q_latent, latents, latents, table, step.positions, step.token_seq, mixed, s.num_heads, 1,
-                              s.latent_dim, s.latent_dim, block_size, s.scale)
-        ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
+        if not (step.is_decode and self._decode_on_tensor_cores(step, q_latent, mixed, latents, table)):
+            ops.attention_general(q_latent, latents, latents, table, step.positions, step.token_seq, mixed, s.num_heads, 1,
+                                  s.latent_dim, s.latent_dim, block_size, s.scale)
         ops.headwise_linear(mixed, self.w_v_up, ctx, s.num_heads, zero_pad=self.ctx_width != self.ctx_dim)
-        ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
+
+    def _decode_on_tensor_cores(self, step, q_latent, mixed, latents, table) -> bool:
+        """One token a sequence in bfloat16: the split decode kernel of the library built for a head as wide as the
+        latent, with all query heads on the one key head.  False where no such library can be built."""
+        s, rt = self.spec, self.rt
+        if (rt.dtype != torch.bfloat16 or rt.device.type != "cuda" or s.latent_dim % 16 != 0 or s.latent_dim > 256
+                or step.cache.block_size % 16 != 0):
+            return False
+        from .attention import decode_splits
+        ops = rt.kernels(s.latent_dim)
+        n = q_latent.shape[0]
+        splits = decode_splits(n, -(-s.num_heads // 16), step.max_ctx, rt.sm_count)
+        scratch_o = scratch_ml = None
+        if splits > 1:
+            scratch_o = rt.workspace.get("attn_split_o", (n * s.num_heads * splits * s.latent_dim,), torch.float32)
+            scratch_ml = rt.workspace.get("attn_split_ml", (n * s.num_heads * splits * 2,), torch.float32)
+        ops.attention_decode(q_latent, latents, latents, table, step.ctx_after, mixed, s.num_heads, 1, s.latent_dim,
+                             step.cache.block_size, s.scale, 0, splits, scratch_o, scratch_ml)
+        return True
+
+    def _attend_expanded(self, step, q, ctx, latents, table, group) -> bool:
+        """A prompt in bfloat16: every head's keys and values are made from the gathered cached vectors by one GEMM,
+        written as pages of a scratch cache, and the tensor-core prompt kernel attends over them as multi-head
+        attention.  False where that kernel does not serve (then the folded way does)."""
+        s, rt = self.spec, self.rt
+        block_size = step.cache.block_size
+        if (step.is_decode or rt.dtype != torch.bfloat16 or rt.device.type != "cuda" or s.head_dim != s.v_head_dim
+                or s.head_dim not in (64, 128) or step.max_q_len <= 32 or block_size & (block_size - 1) or block_size < 16
+                or step.n_seqs * -(-step.max_q_len // 128) > 65535 or self.ctx_width != self.ctx_dim):
+            return False
+        ops_d = rt.kernels(s.head_dim)
+        if not ops_d.has_attention_prefill_tc():
+            return False
+        ops = rt.kernels()
+        meta = step.scratch.get("expanded_context")
+        if meta is None:
+            # every cached position of the step's sequences (this step's included), and a table of scratch pages
+            lengths = [before + new for before, new in zip(step.ctx_before, step.q_lens)]
+            pages = [-(-length // block_size) for length in lengths]
+            width = max(pages)
+            scratch_table = np.zeros((step.n_seqs, width), dtype=np.int32)
+            base = 0
+            for row, count in enumerate(pages):
+                scratch_table[row, :count] = np.arange(base, base + count)
+                base += count
+            host = np.concatenate([np.concatenate([np.arange(length) for length in lengths]),
+                                   np.repeat(np.arange(step.n_seqs), lengths), scratch_table.reshape(-1)]).astype(np.int32)
+            device = torch.from_numpy(host).to(rt.device)
+            total = int(sum(lengths))
+            meta = (total, base, device[:total], device[total:2 * total], device[2 * total:].view(step.n_seqs, width))
+            step.scratch["expanded_context"] = meta
+        total, pages, positions, seqs, scratch_table = meta
+        gathered = rt.workspace.get("latent_rows", (total, s.latent_dim), rt.dtype)
+        ops.paged_gather(latents, table, positions, seqs, gathered)
+        kv_width = s.num_heads * (s.head_dim + s.v_head_dim)
+        expanded = rt.workspace.get("latent_kv", (total, kv_width), torch.float32)
+        ops.linear(gathered, self.w_kv_up, expanded, _ops.MODE_STORE_F32)
+        keys = rt.workspace.get("latent_keys", (pages, s.num_heads, block_size, s.head_dim), rt.dtype)
+        values = rt.workspace.get("latent_values", (pages, s.num_heads, block_size, s.v_head_dim), rt.dtype)
+        # (rows of a sequence's last page beyond its length are never seen, but a weight of zero times whatever the
+        # scratch held, a NaN perhaps, is not zero)
+        values.zero_()
+        ops.qkv_finish(expanded, None, keys, values, positions, seqs, scratch_table, 0, s.num_heads, s.head_dim,
+                       s.v_head_dim, block_size)
+        ops_d.attention_prefill_tc(q, keys, values, scratch_table, step.cu_q, step.ctx_after, ctx, step.max_q_len,
+                                   s.num_heads, s.num_heads, s.head_dim, block_size, s.scale)
+        return True
 
 
 register_mixer("latent_attention", LatentAttention)

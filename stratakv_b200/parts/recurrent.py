@@ -91,7 +91,9 @@ class RgLru(Mixer):
         ops.headwise_linear(u, self.w_gates, gates, s.parts)
         ops.rglru_gates(gates, u, yx, self.y_bias, self.r_bias, self.i_bias, self.lam, self.part)
         mixed = rt.workspace.get("rglru_out", (n, self.padded), rt.dtype, zero=self.padded != c)
-        ops.rglru_scan(gates, yx, self.padded, self.x_bias, mixed, self.part, s.taps, meta, state)
+        need = ops.rglru_scan_scratch(step.n_seqs, step.max_q_len, c)
+        summary = rt.workspace.get("rglru_chunks", (need,), torch.float32) if need else None
+        ops.rglru_scan(gates, yx, self.padded, self.x_bias, mixed, self.part, s.taps, meta, state, step.max_q_len, summary)
         ops.linear(mixed, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
 
 

@@ -28,7 +28,7 @@ class TokenSide(Part):
         s = self.spec
         self.table = self.rt.upload_shared(s.table, tensors[s.table])
         self.w_gate = self.rt.upload(tensors[s.gate_weight]).contiguous()
-        self.w_proj = self.rt.upload(tensors[s.proj_weight]).contiguous()
+        self.w_proj_t = self.rt.upload(tensors[s.proj_weight]).t().contiguous()     # [dim, hidden]
         self.gamma = self.rt.upload(tensors[s.norm_weight], torch.float32)
 
     def forward(self, step, x, next_norm=None, next_out=None) -> None:
@@ -36,7 +36,7 @@ class TokenSide(Part):
         the new stream."""
         s = self.spec
         self.rt.kernels().token_side(
-            x, step.token_ids, self.table, s.offset, s.dim, self.w_gate, self.w_proj, self.gamma, s.eps,
+            x, step.token_ids, self.table, s.offset, s.dim, self.w_gate, self.w_proj_t, self.gamma, s.eps,
             next_gamma=next_norm.gamma if next_norm is not None else None,
             next_eps=next_norm.spec.eps if next_norm is not None else 0.0, next_out=next_out)
 

@@ -189,12 +189,12 @@ class DoubleKernels:
         if next_out is not None:
             next_out.copy_((x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + next_eps) * next_gamma).to(next_out.dtype))
 
-    def token_side(self, x, ids, table, offset, dim, gate_w, proj_w, norm_w, eps, next_gamma=None, next_eps=0.0,
+    def token_side(self, x, ids, table, offset, dim, gate_w, proj_t, norm_w, eps, next_gamma=None, next_eps=0.0,
                    next_out=None):
         self.calls.append("token_side")
         e = table[ids.long()][:, offset:offset + dim].float()
         g = torch.nn.functional.gelu(x @ gate_w.float().T, approximate="tanh") * e
-        self.rmsnorm_add(g @ proj_w.float().T, norm_w, eps, x, next_gamma, next_eps, next_out)
+        self.rmsnorm_add(g @ proj_t.float(), norm_w, eps, x, next_gamma, next_eps, next_out)
 
     def headwise_linear(self, x, w, out, heads, zero_pad=False):
         self.calls.append("headwise_linear")
@@ -233,7 +233,10 @@ class DoubleKernels:
         pairs[:, :, 1, :] = driven
         yx[:, :channels] = torch.nn.functional.gelu(yx[:, :channels] + y_bias, approximate="tanh")
 
-    def rglru_scan(self, gates, yx, x_offset, x_bias, out, part, taps, step_meta, state):
+    def rglru_scan_scratch(self, n_seqs, max_q_len, channels):
+        return 0
+
+    def rglru_scan(self, gates, yx, x_offset, x_bias, out, part, taps, step_meta, state, max_q_len=0, summary=None):
         self.calls.append("rglru_scan")
         positions, token_seq, cu_q, slot_ids = step_meta
         n, channels = gates.shape[0], gates.shape[1] // 2

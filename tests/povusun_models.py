@@ -57,11 +57,12 @@ PB = config(211, 72, [attention(6, 3, 20, 12, 0.6, mlp(100, 0.75)), latent(2, 24
                       rglru(80, 1, 1, None), attention(2, 2, 32, 32, 0.4, mlp(30, 1.0), softcap=3.0, q_temp=(1.0, 64)),
                       attention(6, 3, 20, 12, 0.3, None, softcap=8.0, kv_from=0)], eps=1e-6)
 # PC: head size 64 for keys and values and a latent of 64 and of 128 (the sizes that kernels of one head size serve in
-#     bfloat16), a recurrent layer wider than the model with five taps.
+#     bfloat16; the second latent layer's heads have the size at which prompts run as multi-head attention over
+#     up-projected keys and values), a recurrent layer wider than the model with five taps.
 PC = config(300, 128, [attention(4, 2, 64, 64, 0.25, mlp(136, 1.0), softcap=10.0, q_temp=(0.3, 48)),
                        latent(4, 32, 32, 64, 0.15, mlp(64, 2.0)), rglru(192, 2, 5, mlp(72, 1.0)),
-                       latent(2, 64, 48, 128, 0.1, None),
-                       attention(4, 2, 64, 64, 0.2, mlp(80, 0.5), softcap=10.0, kv_from=0)], side=6)
+                       latent(2, 64, 64, 128, 0.1, None),
+                       attention(4, 2, 64, 64, 0.2, mlp(80, 0.5), softcap=10.0, kv_from=0)], side=16)
 POVUSUN = {"PA": PA, "PB": PB, "PC": PC}
 
 
@@ -80,14 +81,18 @@ def make_folder(folder, raw_config, seed, dtype=torch.float32):
         kind = typed.layers[layer].type if layer is not None else None
         if name.endswith(".mix.lam"):
             tensors[name] = tensors[name] * 10.0 - 2.5           # decays of 0.5 to 0.95 a token
-        elif name.endswith((".b",)) or name.endswith(".mix.conv"):
+        elif name.endswith(".mix.conv"):
+            tensors[name] = tensors[name] * 4.0
+        elif name.endswith((".b",)):
             tensors[name] = tensors[name] * 10.0
         elif kind == "latent_attention" and name.endswith((".mix.q", ".mix.uk")):
             # (no norm on these queries and keys: scores with a standard deviation of 2 to 3)
             tensors[name] = tensors[name] * (sharpen if name.endswith(".mix.q") else sharpen ** 0.5)
         elif name.endswith(".mix.dkv.norm"):
             tensors[name] = 1.0 + (tensors[name] - 1.0) * 8.0     # a latent norm's weight that is far from all ones
-        elif name.endswith((".mix.ra", ".mix.ri", ".mix.g")):
+        elif name.endswith((".mix.ra", ".mix.ri")):
+            tensors[name] = tensors[name] * 2.0
+        elif name.endswith(".mix.g"):
             tensors[name] = tensors[name] * 5.0
         # (the side input's gate stays small: where gelu_tanh of all of a token's few gate values is nearly zero, the
         # norm after the projection blows up what is left of them, rounding included, in any implementation)

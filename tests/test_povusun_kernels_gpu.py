@@ -190,7 +190,7 @@ def test_recurrent_unit_over_portions_batches_and_used_slots(dtype, shape):
     g = torch.Generator().manual_seed(5)
     ops = kernels(dtype)
     P = {name: t.to(dtype).double() for name, t in _recurrent_tensors(width, channels, parts, taps, g).items()}
-    lengths = {"a": 23, "b": 9, "c": 12}
+    lengths = {"a": 23 + 300, "b": 9, "c": 12 + 130}
     inputs = {key: torch.randn(n, width, generator=g).to(dtype).double() for key, n in lengths.items()}
     want = {key: plain.rglru_mixer(h, P, "l0.", {"width": channels}) for key, h in inputs.items()}
     dev32 = lambda t: t.float().contiguous().cuda()
@@ -218,7 +218,10 @@ def test_recurrent_unit_over_portions_batches_and_used_slots(dtype, shape):
             ops.rglru_gates(gates, u, yx, dev32(P["l0.mix.y.b"]), dev32(P["l0.mix.ra.b"].reshape(-1)),
                             dev32(P["l0.mix.ri.b"].reshape(-1)), dev32(P["l0.mix.lam"]), channels // parts)
             out = torch.empty(n, channels, dtype=dtype, device="cuda")
-            ops.rglru_scan(gates, yx, channels, dev32(P["l0.mix.x.b"]), out, channels // parts, taps, meta, state)
+            longest = max(count for _, _, count in parts_of_step)
+            need = ops.rglru_scan_scratch(len(parts_of_step), longest, channels)
+            summary = torch.empty(need, dtype=torch.float32, device="cuda") if need else None
+            ops.rglru_scan(gates, yx, channels, dev32(P["l0.mix.x.b"]), out, channels // parts, taps, meta, state, longest, summary)
         for index, (key, slot, count) in enumerate(parts_of_step):
             got[key][done[key]:done[key] + count] = out[cu[index]:cu[index + 1]].double().cpu()
             done[key] += count
@@ -231,6 +234,7 @@ def test_recurrent_unit_over_portions_batches_and_used_slots(dtype, shape):
     step([("a", 2, 13)])
     step([("c", 0, 1)], twice=True)                 # slot 0 again: its new user starts from nothing
     step([("c", 0, 11)])
+    step([("a", 2, 300), ("c", 0, 130)])            # long enough to be walked in chunks, with unequal last chunks
     for key in lengths:
         assert done[key] == lengths[key]
         close(got[key], want[key], dtype, f"sequence {key}")
@@ -240,7 +244,7 @@ def test_recurrent_unit_over_portions_batches_and_used_slots(dtype, shape):
 def test_norm_that_adds_a_branch_and_the_token_input(dtype):
     g = torch.Generator().manual_seed(6)
     ops = kernels(dtype)
-    for n, hidden, dim in ((1, 64, 8), (37, 72, 5), (9, 640, 24)):
+    for n, hidden, dim in ((1, 64, 8), (37, 72, 5), (9, 640, 24), (301, 2048, 32)):
         x = torch.randn(n, hidden, generator=g) * 2
         y = torch.randn(n, hidden, generator=g) * 5
         gamma = 1.0 + torch.randn(hidden, generator=g) * 0.3
@@ -263,7 +267,7 @@ def test_norm_that_adds_a_branch_and_the_token_input(dtype):
         want = plain.token_side_input(x.double(), tokens, P, "l1.", 1, dim, 1e-5)
         stream = x.clone().cuda()
         ops.token_side(stream, i32(tokens.tolist()), P["side.embed"].to(dtype).cuda(), dim, dim, P["l1.side.gate"].to(dtype).cuda(),
-                       P["l1.side.proj"].to(dtype).cuda(), gamma.cuda(), 1e-5, next_gamma=following.cuda(), next_eps=1e-3, next_out=ahead)
+                       P["l1.side.proj"].to(dtype).t().contiguous().cuda(), gamma.cuda(), 1e-5, next_gamma=following.cuda(), next_eps=1e-3, next_out=ahead)
         close(stream, want, torch.float32, "stream after the token input")
         close(ahead, plain.rms_norm(want, following.double(), 1e-3), dtype, "the next norm after the token input")
 
