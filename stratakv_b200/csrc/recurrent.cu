@@ -31,16 +31,15 @@ struct RecurrentBatch {
     int state_stride;          // floats per slot: (2 + taps) * C
 };
 
-// u[t, c]: one thread per (token, channel).
+// u[t, c]: a block row per token (what is known per token is looked up once a block), threads over the channels.
 __global__ void __launch_bounds__(256)
 rglru_conv_kernel(const float* __restrict__ yx, int row_stride, int x_offset, const float* __restrict__ x_bias,
                   const float* __restrict__ conv_w, const float* __restrict__ conv_b, float* __restrict__ u,
-                  int n_tokens, int channels, int taps, const RecurrentBatch batch) {
+                  int first_token, int channels, int taps, const RecurrentBatch batch) {
     pdl_launch_dependents();
     pdl_wait();
-    const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (item >= (long long)n_tokens * channels) return;
-    const int t = (int)(item / channels), c = (int)(item - (long long)t * channels);
+    const int t = first_token + blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
     const int p = batch.positions[t], s = batch.token_seq[t];
     const int first = batch.cu_q[s];
     const float* ring = batch.state + (size_t)batch.slot_ids[s] * batch.state_stride + 2 * (size_t)channels;
@@ -59,13 +58,20 @@ rglru_conv_kernel(const float* __restrict__ yx, int row_stride, int x_offset, co
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 
+// rate[c] = 8 * softplus(lam[c]): the part of the decay's exponent that does not depend on the token, made once when
+// the weights are loaded.
+__global__ void rglru_rate_kernel(const float* __restrict__ lam, float* __restrict__ rate, int channels) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < channels) rate[c] = RGLRU_DECAY_SCALE * softplus_f(lam[c]);
+}
+
 // Per (token, channel): from the gates' matrix products (gates [tokens, 2C]: per part of `part` channels first the
 // part's r rows, then its i rows) to the decay a and the driven input sqrt(1 - a^2) * i * u, which replace them in
 // place; and the gate branch's activation in place of its pre-activation in yx.
 __global__ void __launch_bounds__(256)
 rglru_gates_kernel(float* __restrict__ gates, const float* __restrict__ u, float* __restrict__ yx, int row_stride,
                    const float* __restrict__ y_bias, const float* __restrict__ r_bias,
-                   const float* __restrict__ i_bias, const float* __restrict__ lam, int n_tokens, int channels,
+                   const float* __restrict__ i_bias, const float* __restrict__ rate, int n_tokens, int channels,
                    int part) {
     pdl_launch_dependents();
     pdl_wait();
@@ -76,7 +82,7 @@ rglru_gates_kernel(float* __restrict__ gates, const float* __restrict__ u, float
     float* pair = gates + (size_t)t * 2 * channels + (size_t)b * 2 * part + within;
     const float r = sigmoid_f(pair[0] + r_bias[c]);
     const float i = sigmoid_f(pair[part] + i_bias[c]);
-    const float a = expf(-RGLRU_DECAY_SCALE * r * softplus_f(lam[c]));
+    const float a = expf(-r * rate[c]);
     pair[0] = a;
     pair[part] = sqrtf(fmaxf(1.0f - a * a, 0.0f)) * i * u[(size_t)t * channels + c];
     float* y = yx + (size_t)t * row_stride + c;
@@ -168,14 +174,26 @@ SKV_EXPORT int skv_rglru_conv(const float* yx, int row_stride, int x_offset, con
     if (int code = check_batch("skv_rglru_conv", positions, token_seq, cu_q, slot_ids, state, state_stride, channels, taps)) return code;
     if (x_offset < 0 || row_stride < x_offset + channels) return fail("skv_rglru_conv", "a row is shorter than its two branches");
     const RecurrentBatch batch = {positions, token_seq, cu_q, slot_ids, state, state_stride};
-    const long long blocks = ((long long)n_tokens * channels + 255) / 256;
-    if (blocks > 0x7fffffffLL) return fail("skv_rglru_conv", "too many tokens in one step");
-    return launch_pdl("skv_rglru_conv", rglru_conv_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, yx, row_stride,
-                      x_offset, x_bias, conv_w, conv_b, u, n_tokens, channels, taps, batch);
+    // (grid.y holds 65,535 rows at most: longer steps go in pieces)
+    for (int done = 0; done < n_tokens; done += 65535) {
+        const int rows = n_tokens - done < 65535 ? n_tokens - done : 65535;
+        if (int code = launch_pdl("skv_rglru_conv", rglru_conv_kernel, dim3((channels + 255) / 256, rows), dim3(256), 0, stream,
+                                  yx, row_stride, x_offset, x_bias, conv_w, conv_b, u, done, channels, taps, batch))
+            return code;
+    }
+    return 0;
 }
 
+// rate [channels] float = 8 * softplus(lam [channels] float).
+SKV_EXPORT int skv_rglru_rate(const float* lam, float* rate, int channels, cudaStream_t stream) {
+    if (channels <= 0) return 0;
+    rglru_rate_kernel<<<(channels + 255) / 256, 256, 0, stream>>>(lam, rate, channels);
+    return check_launch("skv_rglru_rate");
+}
+
+// `rate`: what skv_rglru_rate made of the layer's lam.
 SKV_EXPORT int skv_rglru_gates(float* gates, const float* u, float* yx, int row_stride, const float* y_bias,
-                               const float* r_bias, const float* i_bias, const float* lam, int n_tokens, int channels,
+                               const float* r_bias, const float* i_bias, const float* rate, int n_tokens, int channels,
                                int part, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (channels <= 0 || part <= 0 || channels % part != 0) return fail("skv_rglru_gates", "the channels must split into equal parts");
@@ -183,7 +201,7 @@ SKV_EXPORT int skv_rglru_gates(float* gates, const float* u, float* yx, int row_
     const long long blocks = ((long long)n_tokens * channels + 255) / 256;
     if (blocks > 0x7fffffffLL) return fail("skv_rglru_gates", "too many tokens in one step");
     return launch_pdl("skv_rglru_gates", rglru_gates_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, gates, u, yx,
-                      row_stride, y_bias, r_bias, i_bias, lam, n_tokens, channels, part);
+                      row_stride, y_bias, r_bias, i_bias, rate, n_tokens, channels, part);
 }
 
 constexpr int RGLRU_CHUNK = 64;

@@ -636,19 +636,28 @@ class Kernels:
             _ptr(yx), yx.shape[1], int(x_offset), _ptr(x_bias), _ptr(conv_w), _ptr(conv_b), _ptr(u), n, channels, taps,
             *self._recurrent_batch(step_meta, state, channels, taps, "rglru_conv"), _stream()), "rglru_conv")
 
-    def rglru_gates(self, gates, u, yx, y_bias, r_bias, i_bias, lam, part: int):
+    def rglru_rate(self, lam, rate):
+        """``rate = 8 * softplus(lam)`` (float32, per channel): the token-independent part of the decay's exponent."""
+        self._want(lam, torch.float32, "lam"); self._want(rate, torch.float32, "rate")
+        if lam.numel() != rate.numel():
+            raise KernelError("rglru_rate: sizes differ")
+        self._check(self.lib.skv_rglru_rate(_ptr(lam), _ptr(rate), lam.numel(), _stream()), "rglru_rate")
+        return rate
+
+    def rglru_gates(self, gates, u, yx, y_bias, r_bias, i_bias, rate, part: int):
         """In place: ``gates`` (float32 ``[tokens, 2C]``, per part of ``part`` channels its r rows then its i rows, as
-        ``headwise_linear`` leaves them) becomes the decay ``a = exp(-8 sigmoid(r + r_bias) softplus(lam))`` and the driven
-        input ``sqrt(1 - a^2) sigmoid(i + i_bias) u``; ``yx[:, :C]`` becomes ``gelu_tanh(yx[:, :C] + y_bias)``."""
+        ``headwise_linear`` leaves them) becomes the decay ``a = exp(-sigmoid(r + r_bias) rate)`` (``rate`` from
+        ``rglru_rate``) and the driven input ``sqrt(1 - a^2) sigmoid(i + i_bias) u``; ``yx[:, :C]`` becomes
+        ``gelu_tanh(yx[:, :C] + y_bias)``."""
         self._want(gates, torch.float32, "gates"); self._want(u, torch.float32, "u"); self._want(yx, torch.float32, "yx")
-        for label, tensor in (("y_bias", y_bias), ("r_bias", r_bias), ("i_bias", i_bias), ("lam", lam)):
+        for label, tensor in (("y_bias", y_bias), ("r_bias", r_bias), ("i_bias", i_bias), ("rate", rate)):
             self._want(tensor, torch.float32, label)
         n, channels = u.shape
         if tuple(gates.shape) != (n, 2 * channels) or yx.shape[0] != n or any(
-                t.numel() != channels for t in (y_bias, r_bias, i_bias, lam)):
+                t.numel() != channels for t in (y_bias, r_bias, i_bias, rate)):
             raise KernelError("rglru_gates: shapes do not agree")
         self._check(self.lib.skv_rglru_gates(_ptr(gates), _ptr(u), _ptr(yx), yx.shape[1], _ptr(y_bias), _ptr(r_bias),
-                                             _ptr(i_bias), _ptr(lam), n, channels, int(part), _stream()), "rglru_gates")
+                                             _ptr(i_bias), _ptr(rate), n, channels, int(part), _stream()), "rglru_gates")
 
     def rglru_scan_scratch(self, n_seqs: int, max_q_len: int, channels: int) -> int:
         """Floats of scratch ``rglru_scan`` needs for a step whose longest sequence brings ``max_q_len`` tokens."""

@@ -68,7 +68,9 @@ class RgLru(Mixer):
         as_float = lambda name: rt.upload(tensors[name], torch.float32).reshape(-1).contiguous()
         self.y_bias, self.x_bias = as_float(s.y_bias), as_float(s.x_bias)
         self.conv_w = rt.upload(tensors[s.conv_weight], torch.float32).contiguous()
-        self.conv_b, self.lam = as_float(s.conv_bias), as_float(s.decay)
+        self.conv_b = as_float(s.conv_bias)
+        lam = as_float(s.decay)
+        self.decay_rate = rt.kernels().rglru_rate(lam, torch.empty_like(lam))     # 8 * softplus(lam), once
         self.r_bias, self.i_bias = as_float(s.r_bias), as_float(s.i_bias)
         # per part the r rows, then the i rows: one block-diagonal product makes both gates' inputs
         self.w_gates = torch.cat([rt.upload(tensors[s.r_weight]), rt.upload(tensors[s.i_weight])], dim=1).contiguous()
@@ -89,7 +91,7 @@ class RgLru(Mixer):
         ops.rglru_conv(yx, self.padded, self.x_bias, self.conv_w, self.conv_b, u, meta, state)
         gates = rt.workspace.get("rglru_gates", (n, 2 * c), torch.float32)
         ops.headwise_linear(u, self.w_gates, gates, s.parts)
-        ops.rglru_gates(gates, u, yx, self.y_bias, self.r_bias, self.i_bias, self.lam, self.part)
+        ops.rglru_gates(gates, u, yx, self.y_bias, self.r_bias, self.i_bias, self.decay_rate, self.part)
         mixed = rt.workspace.get("rglru_out", (n, self.padded), rt.dtype, zero=self.padded != c)
         need = ops.rglru_scan_scratch(step.n_seqs, step.max_q_len, c)
         summary = rt.workspace.get("rglru_chunks", (need,), torch.float32) if need else None

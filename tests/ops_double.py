@@ -221,13 +221,17 @@ class DoubleKernels:
                 total = total + conv_w[:, k] * value
             u[t] = total
 
-    def rglru_gates(self, gates, u, yx, y_bias, r_bias, i_bias, lam, part):
+    def rglru_rate(self, lam, rate):
+        rate.copy_(8.0 * torch.nn.functional.softplus(lam))
+        return rate
+
+    def rglru_gates(self, gates, u, yx, y_bias, r_bias, i_bias, rate, part):
         self.calls.append("rglru_gates")
         n, channels = u.shape
         pairs = gates.view(n, channels // part, 2, part)
         r = torch.sigmoid(pairs[:, :, 0, :] + r_bias.view(-1, part))
         i = torch.sigmoid(pairs[:, :, 1, :] + i_bias.view(-1, part))
-        a = torch.exp(-8.0 * r * torch.nn.functional.softplus(lam).view(-1, part))
+        a = torch.exp(-r * rate.view(-1, part))
         driven = torch.sqrt(1.0 - a * a) * i * u.view(n, -1, part)
         pairs[:, :, 0, :] = a
         pairs[:, :, 1, :] = driven

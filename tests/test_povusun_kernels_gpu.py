@@ -195,6 +195,7 @@ def test_recurrent_unit_over_portions_batches_and_used_slots(dtype, shape):
     want = {key: plain.rglru_mixer(h, P, "l0.", {"width": channels}) for key, h in inputs.items()}
     dev32 = lambda t: t.float().contiguous().cuda()
     w_gates = torch.cat([P["l0.mix.ra"], P["l0.mix.ri"]], dim=1).to(dtype).contiguous().cuda()
+    rate = ops.rglru_rate(dev32(P["l0.mix.lam"]), torch.empty(channels, dtype=torch.float32, device="cuda"))
     slots = 4
     state = torch.full((slots + 1, (2 + taps) * channels + 3), 5.0, dtype=torch.float32, device="cuda")   # nobody's zeros
     got = {key: torch.zeros(n, channels, dtype=F64) for key, n in lengths.items()}
@@ -216,7 +217,7 @@ def test_recurrent_unit_over_portions_batches_and_used_slots(dtype, shape):
             gates = torch.empty(n, 2 * channels, dtype=torch.float32, device="cuda")
             ops.headwise_linear(u, w_gates, gates, parts)
             ops.rglru_gates(gates, u, yx, dev32(P["l0.mix.y.b"]), dev32(P["l0.mix.ra.b"].reshape(-1)),
-                            dev32(P["l0.mix.ri.b"].reshape(-1)), dev32(P["l0.mix.lam"]), channels // parts)
+                            dev32(P["l0.mix.ri.b"].reshape(-1)), rate, channels // parts)
             out = torch.empty(n, channels, dtype=dtype, device="cuda")
             longest = max(count for _, _, count in parts_of_step)
             need = ops.rglru_scan_scratch(len(parts_of_step), longest, channels)
