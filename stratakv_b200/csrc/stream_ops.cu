@@ -94,6 +94,17 @@ __global__ void rmsnorm_add_rows_kernel(const float* __restrict__ y, const float
     }
 }
 
+// Four neighbouring weights of a row as floats (the row 8-byte aligned at `p` for bfloat16, 16-byte for float).
+__device__ __forceinline__ void load4(const float* p, float (&out)[4]) {
+    const float4 v = *(const float4*)p;
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&out)[4]) {
+    const uint2 raw = *(const uint2*)p;
+    const float2 lo = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x), hi = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+    out[0] = lo.x; out[1] = lo.y; out[2] = hi.x; out[3] = hi.y;
+}
+
 // A block takes TOK tokens, so that it reads the two weights once for all of them (one token a block where tokens are
 // few, so that there are blocks enough).  `proj_t` is the projection transposed, [dim][hidden], which lets
 // neighbouring threads read neighbouring columns.  VEC: hidden is a multiple of 4 and every row 16-byte aligned; a
@@ -103,7 +114,8 @@ __global__ void __launch_bounds__(TOK == 1 ? 512 : 256) token_side_kernel(float*
                                   int table_stride, int offset, int dim, int vocab, const T* __restrict__ gate_w,
                                   const T* __restrict__ proj_t, const float* __restrict__ norm_w, float eps,
                                   const float* __restrict__ next_gamma, float next_eps, T* __restrict__ next_out,
-                                  int n_tokens, int hidden) {
+                                  int n_tokens, int hidden, const float* __restrict__ branch,
+                                  const float* __restrict__ post_gamma, float post_eps) {
     extern __shared__ __align__(16) float side_shared[];       // [TOK][dim] gated values, [TOK][hidden] projected
     __shared__ float scratch[33];
     pdl_launch_dependents();
@@ -115,7 +127,32 @@ __global__ void __launch_bounds__(TOK == 1 ? 512 : 256) token_side_kernel(float*
     const float* rows[TOK];
 #pragma unroll
     for (int k = 0; k < TOK; ++k) rows[k] = x + (size_t)(t0 + min(k, count - 1)) * hidden;
+    if (branch) {
+        // first the sublayer in front: x += rmsnorm(branch) * post_gamma on this block's rows (rmsnorm_add's work)
+#pragma unroll
+        for (int k = 0; k < TOK; ++k) {
+            const float* y_row = branch + (size_t)(t0 + min(k, count - 1)) * hidden;
+            float sum = 0.0f;
+            for (int c = threadIdx.x; c < hidden; c += blockDim.x) sum = fmaf(y_row[c], y_row[c], sum);
+            const float inverse = 1.0f / sqrtf(block_sum(sum, scratch) / (float)hidden + post_eps);
+            if (k < count) {
+                float* x_row = x + (size_t)(t0 + k) * hidden;
+                for (int c = threadIdx.x; c < hidden; c += blockDim.x) x_row[c] += y_row[c] * inverse * post_gamma[c];
+            }
+        }
+        __syncthreads();                                       // (the rows are read by other threads from here on)
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    if (VEC) {
+        // the block's rows of the stream go to shared memory once (the place of the projected values, which come
+        // later), with every thread's loads in flight together; the gate rows then meet them there
+        const int quads = hidden >> 2;
+        for (int i = threadIdx.x; i < TOK * quads; i += blockDim.x) {
+            const int k = i / quads, q4 = i - k * quads;
+            ((float4*)projected)[i] = *(const float4*)(x + (size_t)(t0 + min(k, count - 1)) * hidden + 4 * q4);
+        }
+        __syncthreads();
+    }
     for (int j0 = 4 * warp; j0 < dim; j0 += 4 * warps) {
         float dot[4][TOK] = {};
         const T* w_rows[4];
@@ -124,16 +161,15 @@ __global__ void __launch_bounds__(TOK == 1 ? 512 : 256) token_side_kernel(float*
         if (VEC) {
 #pragma unroll 2
             for (int c = 4 * lane; c < hidden; c += 128) {
-                float4 xs[TOK];
+                float w[4][4];
 #pragma unroll
-                for (int k = 0; k < TOK; ++k) xs[k] = *(const float4*)(rows[k] + c);
+                for (int jj = 0; jj < 4; ++jj) load4(w_rows[jj] + c, w[jj]);
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                    const float w0 = to_float(w_rows[jj][c]), w1 = to_float(w_rows[jj][c + 1]);
-                    const float w2 = to_float(w_rows[jj][c + 2]), w3 = to_float(w_rows[jj][c + 3]);
+                for (int k = 0; k < TOK; ++k) {
+                    const float4 xs = *(const float4*)(projected + (size_t)k * hidden + c);
 #pragma unroll
-                    for (int k = 0; k < TOK; ++k)
-                        dot[jj][k] += w0 * xs[k].x + w1 * xs[k].y + w2 * xs[k].z + w3 * xs[k].w;
+                    for (int jj = 0; jj < 4; ++jj)
+                        dot[jj][k] += w[jj][0] * xs.x + w[jj][1] * xs.y + w[jj][2] * xs.z + w[jj][3] * xs.w;
                 }
             }
         } else {
@@ -223,7 +259,8 @@ template <int TOK, bool VEC>
 static int launch_token_side(float* x, const int* ids, const void* table, int table_stride, int offset, int dim,
                              int vocab, const void* gate_w, const void* proj_t, const float* norm_w, float eps,
                              const float* next_gamma, float next_eps, void* next_out, int n_tokens, int hidden,
-                             int threads, cudaStream_t stream) {
+                             const float* branch, const float* post_gamma, float post_eps, int threads,
+                             cudaStream_t stream) {
     const size_t smem = (size_t)TOK * (((dim + 3) & ~3) + hidden) * sizeof(float);
     auto kernel = token_side_kernel<skv_t, TOK, VEC>;
     if (smem > 48 * 1024) {
@@ -236,7 +273,7 @@ static int launch_token_side(float* x, const int* ids, const void* table, int ta
     }
     return launch_pdl("skv_token_side", kernel, dim3((n_tokens + TOK - 1) / TOK), dim3(threads), smem, stream, x, ids,
                       (const skv_t*)table, table_stride, offset, dim, vocab, (const skv_t*)gate_w, (const skv_t*)proj_t,
-                      norm_w, eps, next_gamma, next_eps, (skv_t*)next_out, n_tokens, hidden);
+                      norm_w, eps, next_gamma, next_eps, (skv_t*)next_out, n_tokens, hidden, branch, post_gamma, post_eps);
 }
 
 }  // namespace skv
@@ -264,13 +301,16 @@ SKV_EXPORT int skv_rmsnorm_add(const float* y, const float* gamma, float eps, fl
 }
 
 // table [vocab, table_stride], of whose rows the columns offset .. offset + dim - 1 are this layer's; gate_w
-// [dim, hidden]; proj_t [dim, hidden], the projection transposed; norm_w float [hidden].
+// [dim, hidden]; proj_t [dim, hidden], the projection transposed; norm_w float [hidden].  branch and post_gamma
+// (both or neither): x += rmsnorm(branch [n_tokens, hidden] float) * post_gamma comes first, in the same pass.
 SKV_EXPORT int skv_token_side(float* x, const int* ids, const void* table, int table_stride, int offset, int dim,
                               int vocab, const void* gate_w, const void* proj_t, const float* norm_w, float eps,
                               const float* next_gamma, float next_eps, void* next_out, int n_tokens, int hidden,
-                              cudaStream_t stream) {
+                              const float* branch, const float* post_gamma, float post_eps, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hidden <= 0 || dim <= 0 || vocab <= 0) return fail("skv_token_side", "sizes must be positive");
+    if ((branch == nullptr) != (post_gamma == nullptr))
+        return fail("skv_token_side", "a branch needs the weight of the norm it passes on its way into the stream");
     if (offset < 0 || offset + dim > table_stride) return fail("skv_token_side", "the layer's columns lie outside the table");
     if ((next_gamma == nullptr) != (next_out == nullptr))
         return fail("skv_token_side", "the next norm needs its weight and a place for its result");
@@ -283,7 +323,8 @@ SKV_EXPORT int skv_token_side(float* x, const int* ids, const void* table, int t
     const int tok = n_tokens <= 256 ? 1 : (8 * per_token <= 160 * 1024 ? 8 : (4 * per_token <= 200 * 1024 ? 4 : 1));
     const int threads = tok == 1 && hidden >= 1024 ? 512 : 256;      // (the many-token forms keep 100 to 200 registers a thread)
 #define SKV_SIDE(TOK, VEC) launch_token_side<TOK, VEC>(x, ids, table, table_stride, offset, dim, vocab, gate_w, proj_t, norm_w, \
-                                                      eps, next_gamma, next_eps, next_out, n_tokens, hidden, threads, stream)
+                                                      eps, next_gamma, next_eps, next_out, n_tokens, hidden, branch, post_gamma, \
+                                                      post_eps, threads, stream)
     if (tok == 8) return vec ? SKV_SIDE(8, true) : SKV_SIDE(8, false);
     if (tok == 4) return vec ? SKV_SIDE(4, true) : SKV_SIDE(4, false);
     return vec ? SKV_SIDE(1, true) : SKV_SIDE(1, false);

@@ -572,10 +572,12 @@ class Kernels:
                                              ctypes.c_float(next_eps), _ptr(next_out), n, hidden, _stream()), "rmsnorm_add")
 
     def token_side(self, x, ids, table, offset: int, dim: int, gate_w, proj_t, norm_w, eps: float, next_gamma=None,
-                   next_eps: float = 0.0, next_out=None):
+                   next_eps: float = 0.0, next_out=None, branch=None, post_gamma=None, post_eps: float = 0.0):
         """An input that depends on the token, added to the float32 stream: ``e = table[id, offset:offset + dim]``,
         ``g = gelu_tanh(gate_w . x) * e``, ``y = proj_t^T . g`` (``proj_t`` is the projection transposed,
-        ``[dim, hidden]``), ``x += rmsnorm(y) * norm_w``; ``next_*`` as in ``rmsnorm_add``."""
+        ``[dim, hidden]``), ``x += rmsnorm(y) * norm_w``; ``next_*`` as in ``rmsnorm_add``.  With ``branch`` (float32
+        ``[tokens, hidden]``) and ``post_gamma``, ``x += rmsnorm(branch) * post_gamma`` (eps ``post_eps``) comes first: the
+        sublayer in front of the token input is added in the same pass."""
         self._want(x, torch.float32, "x"); self._want(ids, torch.int32, "ids"); self._want(table, self.dtype, "table")
         self._want(gate_w, self.dtype, "gate_w"); self._want(proj_t, self.dtype, "proj_t")
         self._want(norm_w, torch.float32, "norm_w")
@@ -587,10 +589,14 @@ class Kernels:
             self._want(next_out, self.dtype, "next_out"); self._want(next_gamma, torch.float32, "next_gamma")
             if tuple(next_out.shape) != (n, hidden) or next_gamma.numel() != hidden:
                 raise KernelError("token_side: the next norm's shapes do not agree")
+        if branch is not None:
+            self._want(branch, torch.float32, "branch"); self._want(post_gamma, torch.float32, "post_gamma")
+            if tuple(branch.shape) != (n, hidden) or post_gamma.numel() != hidden:
+                raise KernelError("token_side: the branch's shapes do not agree")
         self._check(self.lib.skv_token_side(
             _ptr(x), _ptr(ids), _ptr(table), table.shape[1], int(offset), int(dim), table.shape[0], _ptr(gate_w),
             _ptr(proj_t), _ptr(norm_w), ctypes.c_float(eps), _ptr(next_gamma), ctypes.c_float(next_eps), _ptr(next_out),
-            n, hidden, _stream()), "token_side")
+            n, hidden, _ptr(branch), _ptr(post_gamma), ctypes.c_float(post_eps), _stream()), "token_side")
 
     def headwise_linear(self, x, w, out, heads: int, zero_pad: bool = False):
         """``out[t, h, :] = w[h] . x[t, h, :]`` with ``w`` ``[heads, out_dim, in_dim]`` in the compute dtype; ``x`` and

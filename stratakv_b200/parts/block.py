@@ -145,15 +145,20 @@ def sandwich(layer: Layer, step, x, entry) -> None:
     last = layer.ffn is None and side is None
     ahead_norm = layer.ffn_norm if layer.ffn is not None else (step.next_layer_norm if last else None)
     ahead = add_normed(branch, post_mixer, ahead_norm, "normed" if layer.ffn is not None else "normed_next")
+    pending = None                                  # a branch that the token input's kernel adds on its way
     if layer.ffn is not None:
         h = ahead if ahead is not None else layer.ffn_norm.forward(x)
         branch = _branch(layer.ffn, step, h, tuple(x.shape))
-        ahead_norm = step.next_layer_norm if side is None else None
-        ahead = add_normed(branch, post_ffn, ahead_norm, "normed_next")
+        if side is not None and getattr(side, "adds_branch", False) and _fusable(post_ffn):
+            pending = (branch, post_ffn)
+        else:
+            ahead_norm = step.next_layer_norm if side is None else None
+            ahead = add_normed(branch, post_ffn, ahead_norm, "normed_next")
     if side is not None:
         ahead_norm = step.next_layer_norm
         ahead = normed_ahead(ahead_norm, "normed_next")
-        side.forward(step, x, ahead_norm if ahead is not None else None, ahead)
+        more = dict(branch=pending[0], post_norm=pending[1]) if pending is not None else {}
+        side.forward(step, x, ahead_norm if ahead is not None else None, ahead, **more)
     if ahead is not None and ahead_norm is not None:
         step.scratch["normed_ahead"] = (ahead_norm, ahead)
     if stats is not None:

@@ -190,8 +190,10 @@ class DoubleKernels:
             next_out.copy_((x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + next_eps) * next_gamma).to(next_out.dtype))
 
     def token_side(self, x, ids, table, offset, dim, gate_w, proj_t, norm_w, eps, next_gamma=None, next_eps=0.0,
-                   next_out=None):
+                   next_out=None, branch=None, post_gamma=None, post_eps=0.0):
         self.calls.append("token_side")
+        if branch is not None:
+            self.rmsnorm_add(branch, post_gamma, post_eps, x)
         e = table[ids.long()][:, offset:offset + dim].float()
         g = torch.nn.functional.gelu(x @ gate_w.float().T, approximate="tanh") * e
         self.rmsnorm_add(g @ proj_t.float(), norm_w, eps, x, next_gamma, next_eps, next_out)

@@ -271,6 +271,15 @@ def test_norm_that_adds_a_branch_and_the_token_input(dtype):
                        P["l1.side.proj"].to(dtype).t().contiguous().cuda(), gamma.cuda(), 1e-5, next_gamma=following.cuda(), next_eps=1e-3, next_out=ahead)
         close(stream, want, torch.float32, "stream after the token input")
         close(ahead, plain.rms_norm(want, following.double(), 1e-3), dtype, "the next norm after the token input")
+        # the same with the sublayer in front still to be added: x += rmsnorm(y) * gamma first, in the same kernel
+        before = x.double() + plain.rms_norm(y.double(), following.double(), 1e-4)
+        want = plain.token_side_input(before, tokens, P, "l1.", 1, dim, 1e-5)
+        stream = x.clone().cuda()
+        ops.token_side(stream, i32(tokens.tolist()), P["side.embed"].to(dtype).cuda(), dim, dim, P["l1.side.gate"].to(dtype).cuda(),
+                       P["l1.side.proj"].to(dtype).t().contiguous().cuda(), gamma.cuda(), 1e-5, next_gamma=following.cuda(),
+                       next_eps=1e-3, next_out=ahead, branch=y.cuda(), post_gamma=following.cuda(), post_eps=1e-4)
+        close(stream, want, torch.float32, "stream after a branch and the token input")
+        close(ahead, plain.rms_norm(want, following.double(), 1e-3), dtype, "the next norm after both")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
