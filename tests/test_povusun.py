@@ -83,8 +83,8 @@ def test_bookkeeping_portions_batches_and_slots_used_again(tmp_path, name):
     config, weights = plain_povusun.load_folder(folder)
     engine = cpu_engine(folder, max_tokens=16 * 14, max_batch=3)
     vocab = POVUSUN[name]["vocab"]
-    for round_ in range(2):                   # the second round takes the slots, pages and states of the first
-        prompts = [random_tokens(vocab, n, seed=10 * round_ + n) for n in (5, 40, 18)]
+    for turn in range(2):                     # the second turn takes the slots, pages and states of the first
+        prompts = [random_tokens(vocab, n, seed=10 * turn + n) for n in (5, 40, 18)]
         refs = [plain_povusun.logits_of(config, weights, p).numpy() for p in prompts]
         slots = [engine.open_sequence() for _ in prompts]
         cut = [1, 20, 17]
