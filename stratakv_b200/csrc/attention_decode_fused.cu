@@ -119,10 +119,13 @@ __device__ __forceinline__ uint32_t f_pack(float lo, float hi) {
 // What a design may want done to the new token's queries, key and value before they are used and cached: biases
 // (float, [heads * head_dim], [kv_heads * head_dim] twice; null: none) and, with value_norm, each value head divided
 // by sqrt(mean(v^2) + value_eps).  row_stride: floats from one token's row of qkv to the next (a row may hold more
-// than the queries, keys and values).
+// than the queries, keys and values; one of a layer that does not write the cache may hold its queries only).
+// qk_norm: every query head and the key head divided by sqrt(mean(.^2) + qk_eps) (head sizes that are powers of two);
+// q_temp_every > 0: the queries times 1 + q_temp_coef * ln(floor((position + 1) / q_temp_every) + 1).
 struct NewTokenFinish {
     const float* q_bias; const float* k_bias; const float* v_bias;
     int value_norm; float value_eps; int row_stride;
+    int qk_norm; float qk_eps; float q_temp_coef; int q_temp_every;
 };
 
 __device__ __forceinline__ float4 f_add4(float4 a, const float* bias) {
@@ -169,6 +172,8 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     const int my_end = min(end_group, my_first + per_split);
     const int n_chunks = my_end > my_first ? (my_end - my_first + FWARPS - 1) / FWARPS : 0;
     const float scale_log2 = scale * 1.4426950408889634f;
+    const float cap_log2 = EXTRAS ? extras.softcap * 1.4426950408889634f : 0.0f;
+    const float inverse_cap_log2 = EXTRAS && extras.softcap > 0.0f ? 1.0f / cap_log2 : 0.0f;
     const float* token = qkv + (size_t)seq * (EXTRAS ? finish.row_stride : q_dim + 2 * kv_dim);
     const int newest_group = pos >> 4;
     const bool owns_newest = newest_group >= my_first && newest_group < my_end;
@@ -226,6 +231,9 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
         size_t new_at = 0;
         if (owns_newest)
             new_at = ((size_t)(block_of(pos) * num_kv_heads + kv_head) * block_size + row_in_block(pos)) * FHD;
+        float temperature = 1.0f;
+        if (EXTRAS && finish.q_temp_every > 0)
+            temperature = 1.0f + finish.q_temp_coef * logf((float)((pos + 1) / finish.q_temp_every) + 1.0f);
         for (int i = threadIdx.x; i < items; i += FTHREADS) {
             const int item = i / (HALF / 4), quad = i - item * (HALF / 4);
             const float* x = item < rows ? token + (size_t)(head0 + item) * FHD : token + q_dim + (size_t)kv_head * FHD;
@@ -234,6 +242,18 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                 const float* x_bias = item < rows ? (finish.q_bias ? finish.q_bias + (size_t)(head0 + item) * FHD : nullptr)
                                                   : (finish.k_bias ? finish.k_bias + (size_t)kv_head * FHD : nullptr);
                 if (x_bias) { a = f_add4(a, x_bias + 4 * quad); b = f_add4(b, x_bias + HALF + 4 * quad); }
+                float factor = item < rows ? temperature : 1.0f;
+                if (finish.qk_norm) {
+                    // the HALF / 4 threads of a head are neighbours of one warp, all of them here or none (the
+                    // launcher admits this for head sizes that are powers of two)
+                    const unsigned here = __activemask();
+                    float squares = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+#pragma unroll
+                    for (int offset = HALF / 8; offset > 0; offset >>= 1) squares += __shfl_xor_sync(here, squares, offset);
+                    factor *= 1.0f / sqrtf(squares / (float)FHD + finish.qk_eps);
+                }
+                a = make_float4(a.x * factor, a.y * factor, a.z * factor, a.w * factor);
+                b = make_float4(b.x * factor, b.y * factor, b.z * factor, b.w * factor);
             }
             const float xa[4] = {a.x, a.y, a.z, a.w}, xb[4] = {b.x, b.y, b.z, b.w};
             float first[4], second[4];
@@ -342,6 +362,8 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                     float v = (key < ctx && key >= lo) ? s[t][e] * scale_log2 : -INFINITY;
                     if (EXTRAS && extras.bias && key < ctx && key >= lo && g + 8 * (e >> 1) < rows)
                         v -= __ldg(extras.bias + (size_t)(head0 + g + 8 * (e >> 1)) * extras.bias_len + min(pos - key, extras.bias_len - 1));
+                    // (capped: in units of log2; a masked score stays -infinity)
+                    if (EXTRAS && extras.softcap > 0.0f && v != -INFINITY) v = cap_log2 * tanh_by_exp2(v * inverse_cap_log2);
                     s[t][e] = v;
                     tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
                 }
@@ -452,7 +474,8 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
             total += weight * slots[b * FPITCH + d];
             sum += weight * slots[b * FPITCH + FHD + 1];
         }
-        out[((size_t)seq * num_heads + head0 + r) * FHD + d] = __float2bfloat16_rn(EXTRAS ? total / sum * gate_factor(extras, seq, head0 + r) : total / sum);
+        out[((size_t)seq * num_heads + head0 + r) * FHD + d] = __float2bfloat16_rn(
+            EXTRAS ? total / sum * gate_factor(extras, seq, head0 + r) * gate_element(extras, seq, head0 + r, FHD, d) : total / sum);
     }
 }
 
@@ -472,19 +495,26 @@ SKV_EXPORT int skv_attention_decode_fused_extras(const float* qkv, int row_strid
                                                  int num_kv_heads, int head_dim, int block_size, float scale, int window,
                                                  int splits, int write_kv, const float* q_bias, const float* k_bias,
                                                  const float* v_bias, int value_norm, float value_eps, const float* bias,
-                                                 int bias_len, const float* gate, int gate_stride, cudaStream_t stream) {
+                                                 int bias_len, const float* gate, int gate_stride, int qk_norm,
+                                                 float qk_eps, float q_temp_coef, int q_temp_every, float softcap,
+                                                 int gate_per_element, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     const int row_floats = (num_heads + 2 * num_kv_heads) * head_dim;
     if (row_stride == 0) row_stride = row_floats;
-    if (row_stride < row_floats || row_stride % 4 != 0)
+    // (a layer that does not write the cache reads its queries only)
+    if (row_stride < (write_kv ? row_floats : num_heads * head_dim) || row_stride % 4 != 0)
         return fail("skv_attention_decode_fused", "a row of qkv must hold its queries, keys and values and be a multiple of 16 bytes");
     if (value_norm && head_dim > 128) return fail("skv_attention_decode_fused", "the value norm is built for head sizes up to 128");
-    if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads))
-        return fail("skv_attention_decode_fused", "a bias table needs its length and a gate rows of at least heads numbers");
+    if (qk_norm && (head_dim & (head_dim - 1)) != 0)
+        return fail("skv_attention_decode_fused", "the unit norm of queries and keys is built for head sizes that are powers of two");
+    if (q_temp_every < 0 || softcap < 0.0f) return fail("skv_attention_decode_fused", "a temperature's period and a cap must not be negative");
+    if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads * (gate_per_element ? head_dim : 1)) || (gate_per_element && !gate))
+        return fail("skv_attention_decode_fused", "a bias table needs its length and a gate rows of at least heads numbers (heads * head_dim with a gate per number)");
     if (((uintptr_t)q_bias | (uintptr_t)k_bias | (uintptr_t)v_bias) & 15)
         return fail("skv_attention_decode_fused", "biases must be 16-byte aligned");
-    const NewTokenFinish finish = {q_bias, k_bias, v_bias, value_norm, value_eps, row_stride};
-    const AttentionExtras extras = {bias, bias_len, gate, gate_stride};
+    const NewTokenFinish finish = {q_bias, k_bias, v_bias, value_norm, value_eps, row_stride,
+                                   qk_norm, qk_eps, q_temp_coef, q_temp_every};
+    const AttentionExtras extras = {bias, bias_len, gate, gate_stride, softcap, gate_per_element};
     if (head_dim != FHD) return fail("skv_attention_decode_fused", "this library was built for another head size");
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_decode_fused", "heads must be a positive multiple of kv heads");
@@ -535,7 +565,8 @@ SKV_EXPORT int skv_attention_decode_fused_extras(const float* qkv, int row_strid
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = pdl_enabled() ? 2 : 1;
-    const bool any_extras = q_bias || k_bias || v_bias || value_norm || bias || gate || row_stride != row_floats;
+    const bool any_extras = q_bias || k_bias || v_bias || value_norm || bias || gate || row_stride != row_floats ||
+                            qk_norm || q_temp_every > 0 || softcap > 0.0f;
     const cudaError_t status = cudaLaunchKernelEx(
         &config, any_extras ? decode_attention_fused_kernel<true> : decode_attention_fused_kernel<false>, qkv, (const float2*)cos_sin, (__nv_bfloat16*)k_cache,
         (__nv_bfloat16*)v_cache, block_table, table_width, ctx_after, (__nv_bfloat16*)out, num_heads, num_kv_heads,
@@ -551,7 +582,8 @@ SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin
                                           cudaStream_t stream) {
     return skv_attention_decode_fused_extras(qkv, 0, cos_sin, k_cache, v_cache, block_table, table_width, ctx_after, out,
                                              n_seqs, num_heads, num_kv_heads, head_dim, block_size, scale, window, splits,
-                                             write_kv, nullptr, nullptr, nullptr, 0, 0.0f, nullptr, 0, nullptr, 0, stream);
+                                             write_kv, nullptr, nullptr, nullptr, 0, 0.0f, nullptr, 0, nullptr, 0, 0, 0.0f, 0.0f, 0,
+                                             0.0f, 0, stream);
 }
 
 SKV_EXPORT int skv_has_attention_decode_fused() { return 1; }
@@ -567,7 +599,7 @@ SKV_EXPORT int skv_attention_decode_fused(const float*, const float*, void*, voi
 SKV_EXPORT int skv_attention_decode_fused_extras(const float*, int, const float*, void*, void*, const int*, int, const int*,
                                                  void*, int, int, int, int, int, float, int, int, int, const float*,
                                                  const float*, const float*, int, float, const float*, int, const float*,
-                                                 int, cudaStream_t) {
+                                                 int, int, float, float, int, float, int, cudaStream_t) {
     return skv::fail("skv_attention_decode_fused",
                      "this kernel exists in the bfloat16 build for head sizes up to 192 only");
 }

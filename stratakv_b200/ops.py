@@ -394,21 +394,25 @@ class Kernels:
     def attention_decode_fused(self, qkv, cos_sin, k_cache, v_cache, block_table, ctx_after, out, num_heads: int,
                                num_kv_heads: int, head_dim: int, block_size: int, scale: float, window: int = 0,
                                splits: int = 1, write_kv: bool = True, q_bias=None, k_bias=None, v_bias=None,
-                               value_norm_eps=None, bias=None, gate=None, gate_stride: int = 0):
+                               value_norm_eps=None, bias=None, gate=None, gate_stride: int = 0, qk_norm_eps=None,
+                               q_temperature=None, softcap: float = 0.0, gate_per_element: bool = False):
         """One new token per sequence (bfloat16 build), from the float32 q|k|v projection: rotates queries
         and the new key (``cos_sin`` table, or ``None`` for no rotation), writes the new key and value into
         the cache, attends over ``ctx_after[s]`` keys and merges ``splits`` (1..8) context pieces in-kernel.
         A row of ``qkv`` may be wider than its queries, keys and values.  Optional: float32 biases on the three,
         each value head divided by its root mean square (``value_norm_eps``), and ``bias``/``gate`` as in
-        ``attention_prefill``."""
+        ``attention_prefill``; ``qk_norm_eps``: every query head and the new key head divided by its root mean square
+        (head sizes that are powers of two); ``q_temperature`` ``(coef, every)``, ``softcap`` and ``gate_per_element`` as
+        in ``qkv_finish`` and ``attention_prefill_tc``.  With ``write_kv`` false a row need hold its queries only."""
         self._want(qkv, torch.float32, "qkv"); self._want(out, self.dtype, "out")
         self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
         self._want(block_table, torch.int32, "block_table"); self._want(ctx_after, torch.int32, "ctx_after")
         if cos_sin is not None:
             self._want(cos_sin, torch.float32, "cos_sin")
         n = qkv.shape[0]
-        if qkv.shape[1] < (num_heads + 2 * num_kv_heads) * head_dim:
+        if qkv.shape[1] < (num_heads + (2 * num_kv_heads if write_kv else 0)) * head_dim:
             raise KernelError("attention_decode_fused: a row of qkv is shorter than its queries, keys and values")
+        coef, every = q_temperature if q_temperature is not None else (0.0, 0)
         if ctx_after.numel() != n or block_table.shape[0] != n:
             raise KernelError("attention_decode_fused: one length and one table row per sequence is needed")
         for name, vector, width in (("q_bias", q_bias, num_heads * head_dim), ("k_bias", k_bias, num_kv_heads * head_dim),
@@ -422,8 +426,9 @@ class Kernels:
             _ptr(ctx_after), _ptr(out), n, num_heads, num_kv_heads, head_dim, block_size, ctypes.c_float(scale),
             window, splits, int(bool(write_kv)), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
             int(value_norm_eps is not None), ctypes.c_float(value_norm_eps or 0.0),
-            *self._extras(bias, gate, gate_stride, num_heads, "attention_decode_fused"), _stream()),
-            "attention_decode_fused")
+            *self._extras(bias, gate, gate_stride, num_heads, "attention_decode_fused", head_dim if gate_per_element else 0),
+            int(qk_norm_eps is not None), ctypes.c_float(qk_norm_eps or 0.0), ctypes.c_float(coef), int(every),
+            ctypes.c_float(softcap), int(bool(gate_per_element)), _stream()), "attention_decode_fused")
 
     def embed_sum(self, table, ids, out, positions, token_seq, cu_q, slot_ids, flag=None, pair_table=None,
                   last_ids=None, mul_prev: int = 0, mul_cur: int = 0, position_table=None,

@@ -188,9 +188,7 @@ class PagedAttention(Mixer):
         ops.linear(h, self.w_qkv, fused, _ops.MODE_STORE_F32)
         k_cache, v_cache = step.cache.entry_kv(cache_entry)
         table = step.block_tables[step.cache.entry_group_index(cache_entry)]
-        if step.is_decode and self._specialised() and not s.needs_general_kernels:
-            # (the kernel that finishes the new token itself knows biases and the value norm, not the unit norms,
-            # the temperature or rows without keys: those go through qkv_finish and the split kernel)
+        if step.is_decode and self._specialised():
             ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
             if self._decode_fused(step, fused, ctx, k_cache, v_cache, table, writes_cache):
                 ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
@@ -222,6 +220,8 @@ class PagedAttention(Mixer):
         block_size = step.cache.block_size
         if not ops.has_attention_decode_fused() or s.head_dim > 128 or block_size % 16 != 0:
             return False
+        if s.qk_norm_eps is not None and s.head_dim & (s.head_dim - 1):
+            return False                            # (the kernel's unit norm wants a head size that is a power of two)
         n = fused.shape[0]
         blocks_per_seq = s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16))
         keys = min(step.max_ctx, s.window) if s.window > 0 else step.max_ctx
@@ -229,10 +229,13 @@ class PagedAttention(Mixer):
         if wants_more_pieces(n, blocks_per_seq, keys, splits, rt.sm_count):
             return False
         ops.attention_decode_fused(fused, None, k_cache, v_cache, table, step.ctx_after, ctx, s.num_heads, s.num_kv_heads,
-                                   s.head_dim, block_size, s.scale, s.window, splits, writes_cache,
+                                   s.head_dim, block_size, s.scale, s.window, splits, writes_cache and not s.shares_kv,
                                    q_bias=self.q_bias, k_bias=self.k_bias, v_bias=self.v_bias,
                                    value_norm_eps=s.value_norm_eps, bias=self.bias_table,
-                                   gate=fused[:, self.gate_offset:] if s.gate_weight else None, gate_stride=self.fused_width)
+                                   gate=fused[:, self.gate_offset:] if s.gate_weight else None, gate_stride=self.fused_width,
+                                   qk_norm_eps=s.qk_norm_eps,
+                                   q_temperature=(s.q_temperature.coef, s.q_temperature.every) if s.q_temperature else None,
+                                   softcap=s.softcap, gate_per_element=s.gate_per_element)
         return True
 
     def _attend_specialised(self, step, q, ctx, k_cache, v_cache, table, gate) -> bool:

@@ -98,12 +98,6 @@ class AttentionSpec:
                     or self.v_bias or self.value_norm_eps is not None or self.distance_bias or self.gate_weight
                     or self.qk_norm_eps is not None or self.q_temperature or self.softcap or self.shares_kv)
 
-    @property
-    def needs_general_kernels(self) -> bool:
-        """True if a mechanism is in use that only the kernels with run-time head sizes implement."""
-        return bool(self.qk_norm_eps is not None or self.q_temperature or self.softcap or self.shares_kv
-                    or self.gate_per_element)
-
 
 @dataclass(frozen=True)
 class LatentAttentionSpec:
