@@ -301,3 +301,71 @@ def test_clamped_gated_unit_on_every_projection_kernel(dtype):
         out = torch.empty(n, packed.shape[0] // 2, dtype=dtype, device="cuda")
         ops.linear(h.cuda(), packed, out, _ops.MODE_GATED, "swiglu_clamp", activation_param=limit)
         close(out[:, :ff], want, dtype, f"{n} tokens")
+
+
+@pytest.mark.parametrize("head_dim", [32, 64])
+def test_fused_decode_attention_finishes_the_new_token(head_dim):
+    """One token a sequence, straight from the float32 projection: unit norms of the queries and the new key, the
+    temperature, the cap, the gate per number; then the same for a layer that borrows its keys (rows with queries
+    only, the newest key and value read from the cache)."""
+    from stratakv_b200.parts.attention import fused_decode_splits
+    dtype = torch.bfloat16
+    ops = kernels(dtype, head_dim)
+    if not ops.has_attention_decode_fused():
+        pytest.skip("no fused decode kernel in this build")
+    g = torch.Generator().manual_seed(8)
+    heads, kv_heads, block, eps, cap, coef, every, scale = 4, 2, 16, 1e-4, 4.0, 0.5, 7, 0.3
+    lengths = [130, 65, 14]                                  # positions 129, 64 and 13 are the new ones (14 = 2 * 7)
+    n = len(lengths)
+    q_dim, kv_dim = heads * head_dim, kv_heads * head_dim
+    table = scrambled_table(n, 9, g)
+    k_cache = torch.zeros(n * 9 + 2, kv_heads, block, head_dim, dtype=dtype, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    old_k = [plain.unit_rms(torch.randn(length - 1, kv_heads, head_dim, generator=g).double(), eps).to(dtype).double() for length in lengths]
+    old_v = [torch.randn(length - 1, kv_heads, head_dim, generator=g).to(dtype).double() for length in lengths]
+    for s, length in enumerate(lengths):
+        for t in range(length - 1):
+            k_cache[int(table[s, t // block]), :, t % block] = old_k[s][t].to(dtype).cuda()
+            v_cache[int(table[s, t // block]), :, t % block] = old_v[s][t].to(dtype).cuda()
+    rows = torch.randn(n, q_dim + 2 * kv_dim + q_dim + 8, generator=g) * 2        # [q | k | v | gate | padding]
+    gate_at = q_dim + 2 * kv_dim
+
+    def expected(s, q_row, k_all, v_all, gate_row):
+        pos = lengths[s] - 1
+        q = plain.unit_rms(q_row.double().view(heads, head_dim), eps) * plain.query_temperature(torch.tensor([pos]), coef, every)
+        q = q.to(dtype).double()
+        scores = torch.einsum("hd,jhd->hj", q, k_all.repeat_interleave(heads // kv_heads, dim=1)) * scale
+        weights = torch.softmax(plain.soft_cap(scores, cap), dim=-1)
+        out = torch.einsum("hj,jhd->hd", weights, v_all.repeat_interleave(heads // kv_heads, dim=1)).reshape(-1)
+        return out * torch.sigmoid(gate_row.double())
+
+    ctx_after = i32(lengths)
+    out = torch.empty(n, q_dim, dtype=dtype, device="cuda")
+    splits = fused_decode_splits(n, kv_heads, max(lengths), 148)
+    fused = rows.cuda()
+    ops.attention_decode_fused(fused, None, k_cache, v_cache, table.cuda(), ctx_after, out, heads, kv_heads, head_dim, block,
+                               scale, 0, splits, True, gate=fused[:, gate_at:], gate_stride=rows.shape[1], qk_norm_eps=eps,
+                               q_temperature=(coef, every), softcap=cap, gate_per_element=True)
+    new_k, new_v = [], []
+    for s, length in enumerate(lengths):
+        k_new = plain.unit_rms(rows[s, q_dim:q_dim + kv_dim].double().view(kv_heads, head_dim), eps).to(dtype).double()
+        v_new = rows[s, q_dim + kv_dim:q_dim + 2 * kv_dim].view(kv_heads, head_dim).to(dtype).double()
+        new_k.append(k_new); new_v.append(v_new)
+        pos = length - 1
+        close(k_cache[int(table[s, pos // block]), :, pos % block], k_new, dtype, f"cached key of sequence {s}")
+        close(v_cache[int(table[s, pos // block]), :, pos % block], v_new, dtype, f"cached value of sequence {s}")
+        want = expected(s, rows[s, :q_dim], torch.cat([old_k[s], k_new[None]]), torch.cat([old_v[s], v_new[None]]),
+                        rows[s, gate_at:gate_at + q_dim])
+        close(out[s], want, dtype, f"sequence {s}")
+    # a layer that borrows these keys: rows [q | gate], nothing written
+    borrowed = torch.randn(n, 2 * q_dim, generator=g) * 2
+    before = k_cache.clone()
+    fused = borrowed.cuda()
+    ops.attention_decode_fused(fused, None, k_cache, v_cache, table.cuda(), ctx_after, out, heads, kv_heads, head_dim, block,
+                               scale, 0, splits, False, gate=fused[:, q_dim:], gate_stride=2 * q_dim, qk_norm_eps=eps,
+                               q_temperature=(coef, every), softcap=cap, gate_per_element=True)
+    assert torch.equal(k_cache, before)
+    for s in range(n):
+        want = expected(s, borrowed[s, :q_dim], torch.cat([old_k[s], new_k[s][None]]), torch.cat([old_v[s], new_v[s][None]]),
+                        borrowed[s, q_dim:])
+        close(out[s], want, dtype, f"borrowing sequence {s}")
