@@ -137,7 +137,8 @@ class LatentAttention(Mixer):
         block_size = step.cache.block_size
         if (step.is_decode or rt.dtype != torch.bfloat16 or rt.device.type != "cuda" or s.head_dim != s.v_head_dim
                 or s.head_dim not in (64, 128) or step.max_q_len <= 32 or block_size & (block_size - 1) or block_size < 16
-                or step.n_seqs * -(-step.max_q_len // 128) > 65535 or self.ctx_width != self.ctx_dim):
+                or step.n_seqs * -(-step.max_q_len // 128) > 65535 or self.ctx_width != self.ctx_dim
+                or s.latent_dim % 8 != 0):          # (the up-projection GEMM reads rows of whole 16 bytes)
             return False
         ops_d = rt.kernels(s.head_dim)
         if not ops_d.has_attention_prefill_tc():
